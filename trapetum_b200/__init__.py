@@ -31,6 +31,10 @@ def _host(host, config) -> str:
     Python.  "auto" (the default; or $TRAPETUM_HOST): native where the model allows it, else python."""
     host = host or _os.environ.get("TRAPETUM_HOST") or "auto"
     if host == "auto":
+        from .config.base import architecture, architecture_name, read_config_dict
+        d = config if isinstance(config, dict) else read_config_dict(config)
+        if not architecture(architecture_name(d)).native:
+            return "python"                           # no need to build the native library to learn that
         from . import native
         return "native" if native.is_native(load_config(config)[1]) else "python"
     if host not in HOSTS:

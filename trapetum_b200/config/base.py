@@ -175,11 +175,12 @@ class ArchitectureEntry:
     name: str
     config_cls: type
     to_spec: Any  # callable(config) -> ModelSpec
+    native: bool = True   # False: some part has no class on the native host, so it need not be asked
 
 
-def register_architecture(name: str, config_cls: type, to_spec) -> None:
-    """Make ``architectures[0] == name`` in a config.json select this model."""
-    _ARCHITECTURES[name] = ArchitectureEntry(name, config_cls, to_spec)
+def register_architecture(name: str, config_cls: type, to_spec, native: bool = True) -> None:
+    """Make ``architectures[0] == name`` (or ``architecture == name``) in a config.json select this model."""
+    _ARCHITECTURES[name] = ArchitectureEntry(name, config_cls, to_spec, native)
 
 
 def known_architectures() -> List[str]:
@@ -210,8 +211,11 @@ def read_config_dict(path: str) -> Dict[str, Any]:
 
 def architecture_name(d: Dict[str, Any]) -> str:
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        return d["architecture"]                      # the one-name spelling
     if not (isinstance(archs, list) and archs and isinstance(archs[0], str)):
-        raise ConfigError("config.json: key 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: key 'architectures' must be a non-empty list of names "
+                          "(or 'architecture' one name)")
     return archs[0]
 
 

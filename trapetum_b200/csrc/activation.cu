@@ -4,12 +4,19 @@
 // reference computes in gelu_mul_k (runtime/cuda/codebook_gemv.cu:531-537); silu
 // is there for arrangements that want it (codebook_gemv.cu:205-209).  The input
 // holds gate in columns [0, I) and up in [I, 2I) of each row; all math is 32-bit.
+//
+// clamped_swish is the gate of feed-forwards that bound both branches by a limit L:
+//   g' = min(g, L), u' = clamp(u, -L, L), out = g' sigmoid(1.702 g') (u' + 1).
+//
+// Also here: the per-token gate of a token-indexed side input (tb_token_gate), a plain scale
+// (tb_scale) and the bias row (tb_add_bias).
 #include "common.cuh"
 
 TB_EXPORT_ERROR()
 
 #define ACT_GELU_TANH 0
 #define ACT_SILU 1
+#define ACT_CLAMPED_SWISH 2
 
 __device__ __forceinline__ float gelu_tanh_f(float g) {
     return 0.5f * g * (1.0f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)));
@@ -17,7 +24,7 @@ __device__ __forceinline__ float gelu_tanh_f(float g) {
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
 
 template <typename TI, typename TO, int ACT>
-__global__ void gated_act_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int inter) {
+__global__ void gated_act_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int inter, float limit) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t row = blockIdx.x;
@@ -25,21 +32,27 @@ __global__ void gated_act_kernel(const TI* __restrict__ gu, TO* __restrict__ out
     if (c >= inter) return;
     const float g = to_f<TI>(gu[row * 2 * inter + c]);
     const float u = to_f<TI>(gu[row * 2 * inter + inter + c]);
+    if (ACT == ACT_CLAMPED_SWISH) {
+        const float gc = fminf(g, limit), uc = fminf(fmaxf(u, -limit), limit);
+        out[row * inter + c] = from_f<TO>(gc / (1.0f + expf(-1.702f * gc)) * (uc + 1.0f));
+        return;
+    }
     const float a = (ACT == ACT_GELU_TANH) ? gelu_tanh_f(g) : silu_f(g);
     out[row * inter + c] = from_f<TO>(a * u);
 }
 
-extern "C" int tb_gated_act(const void* gu, int in_dtype, void* out, int out_dtype, int rows, int inter,
-                            int act, cudaStream_t stream) {
+static int gated_act_launch(const void* gu, int in_dtype, void* out, int out_dtype, int rows, int inter,
+                            int act, float limit, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (inter <= 0) return tb_refuse("gated_act: intermediate size %d", inter);
-    if (act != ACT_GELU_TANH && act != ACT_SILU) return tb_refuse("gated_act: unknown activation %d", act);
+    if (act < ACT_GELU_TANH || act > ACT_CLAMPED_SWISH) return tb_refuse("gated_act: unknown activation %d", act);
     dim3 grid(rows, (inter + 255) / 256);
     if (grid.y > 65535) return tb_refuse("gated_act: intermediate size %d is too wide", inter);
 #define LAUNCH(TI, TO)                                                                         \
     do {                                                                                       \
-        if (act == ACT_GELU_TANH) tb_launch(gated_act_kernel<TI, TO, ACT_GELU_TANH>, dim3(grid), dim3(256), 0, stream, (const TI*)gu, (TO*)out, inter); \
-        else tb_launch(gated_act_kernel<TI, TO, ACT_SILU>, dim3(grid), dim3(256), 0, stream, (const TI*)gu, (TO*)out, inter);                       \
+        if (act == ACT_GELU_TANH) tb_launch(gated_act_kernel<TI, TO, ACT_GELU_TANH>, dim3(grid), dim3(256), 0, stream, (const TI*)gu, (TO*)out, inter, limit); \
+        else if (act == ACT_SILU) tb_launch(gated_act_kernel<TI, TO, ACT_SILU>, dim3(grid), dim3(256), 0, stream, (const TI*)gu, (TO*)out, inter, limit); \
+        else tb_launch(gated_act_kernel<TI, TO, ACT_CLAMPED_SWISH>, dim3(grid), dim3(256), 0, stream, (const TI*)gu, (TO*)out, inter, limit); \
     } while (0)
     if (in_dtype == TB_F32 && out_dtype == TB_F32) LAUNCH(float, float);
     else if (in_dtype == TB_F32 && out_dtype == TB_BF16) LAUNCH(float, bf16);
@@ -47,6 +60,62 @@ extern "C" int tb_gated_act(const void* gu, int in_dtype, void* out, int out_dty
     else if (in_dtype == TB_BF16 && out_dtype == TB_F32) LAUNCH(bf16, float);
     else return tb_refuse("gated_act: unknown dtype codes %d %d", in_dtype, out_dtype);
 #undef LAUNCH
+    return tb_launch_status();
+}
+
+extern "C" int tb_gated_act(const void* gu, int in_dtype, void* out, int out_dtype, int rows, int inter,
+                            int act, cudaStream_t stream) {
+    if (act == ACT_CLAMPED_SWISH) return tb_refuse("gated_act: this activation needs its limit (tb_gated_act_limit)");
+    return gated_act_launch(gu, in_dtype, out, out_dtype, rows, inter, act, 0.f, stream);
+}
+
+// The same with the activation's parameter (the limit of clamped_swish).
+extern "C" int tb_gated_act_limit(const void* gu, int in_dtype, void* out, int out_dtype, int rows, int inter,
+                                  int act, float limit, cudaStream_t stream) {
+    return gated_act_launch(gu, in_dtype, out, out_dtype, rows, inter, act, limit, stream);
+}
+
+// out[t, j] = gelu_tanh(g[t, j]) * table[ids[t], col0 + j]: the gate of a side input that is looked up by token id.
+template <typename TI, typename TW, typename TO>
+__global__ void token_gate_kernel(const TI* __restrict__ g, const int* __restrict__ ids, const TW* __restrict__ table,
+                                  long long table_stride, int col0, int vocab, TO* __restrict__ out, int dim) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    const int j = blockIdx.y * blockDim.x + threadIdx.x;
+    if (j >= dim) return;
+    const int id = ids[t];
+    const float e = (id >= 0 && id < vocab) ? to_f<TW>(table[(size_t)id * table_stride + col0 + j]) : __int_as_float(0x7fc00000);
+    out[t * dim + j] = from_f<TO>(gelu_tanh_f(to_f<TI>(g[t * dim + j])) * e);
+}
+
+extern "C" int tb_token_gate(const void* g, int g_dtype, const int* ids, const void* table, int table_dtype,
+                             long long table_stride, int col0, int vocab, void* out, int rows, int dim, cudaStream_t stream) {
+    if (rows <= 0 || dim <= 0) return 0;
+    dim3 grid(rows, (dim + 127) / 128);
+    if (grid.y > 65535) return tb_refuse("token_gate: dim %d is too wide", dim);
+#define LAUNCH(TI, TW) tb_launch(token_gate_kernel<TI, TW, TI>, dim3(grid), dim3(128), 0, stream, (const TI*)g, ids, \
+                                 (const TW*)table, table_stride, col0, vocab, (TI*)out, dim)
+    if (g_dtype == TB_F32 && table_dtype == TB_F32) LAUNCH(float, float);
+    else if (g_dtype == TB_F32 && table_dtype == TB_BF16) LAUNCH(float, bf16);
+    else if (g_dtype == TB_BF16 && table_dtype == TB_BF16) LAUNCH(bf16, bf16);
+    else if (g_dtype == TB_BF16 && table_dtype == TB_F32) LAUNCH(bf16, float);
+    else return tb_refuse("token_gate: unknown dtype codes %d %d", g_dtype, table_dtype);
+#undef LAUNCH
+    return tb_launch_status();
+}
+
+// x *= s in place (32-bit).
+__global__ void scale_kernel(float* __restrict__ x, float s, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] *= s;
+}
+
+extern "C" int tb_scale(float* x, float s, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    tb_launch(scale_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, s, (size_t)n);
     return tb_launch_status();
 }
 

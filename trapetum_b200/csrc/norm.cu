@@ -471,3 +471,84 @@ extern "C" int tb_residual_add(float* h, const void* a, int a_dtype, long long n
     TB_DISPATCH_1(a_dtype, TA, tb_launch(add_kernel<TA>, dim3(blocks), dim3(256), 0, stream, h, (const TA*)a, (size_t)n));
     return tb_launch_status();
 }
+
+// Norm after the sum, and the sum with a normed branch, each with an optional copy of the new row in the compute
+// dtype (for arrangements whose sublayers read the stream itself and not a normed copy of it):
+//
+//   POST:   h <- (alpha h + a) * rsqrt(mean((alpha h + a)^2) + eps) * (offset + w)
+//   else:   h <- h + a * rsqrt(mean(a^2) + eps) * (offset + w)
+//   then, if asked:  out = h rounded to the compute dtype
+//
+// `a` may be split-K partial sums, added in split order.  One CTA per row, the row's sums kept in shared memory
+// between the two passes when they fit.  Everything is 32-bit.
+template <typename TA, typename TW, typename TO, bool POST>
+__global__ void fold_rmsnorm_kernel(float* __restrict__ h, float alpha, const TA* __restrict__ a, int n_splits,
+                                    long long split_stride, const TW* __restrict__ w, float eps, float offset,
+                                    TO* __restrict__ out, int width, int row_cache) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(16) float row[];
+    __shared__ float red[33];
+    const size_t base = (size_t)blockIdx.x * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v[1];
+        load_sum<TA, 1>(a + base + i, n_splits, split_stride, v);
+        if (POST) v[0] = alpha * h[base + i] + v[0];
+        if (row_cache) row[i] = v[0];
+        ss += v[0] * v[0];
+    }
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v[1];
+        if (row_cache) v[0] = row[i];
+        else {
+            load_sum<TA, 1>(a + base + i, n_splits, split_stride, v);
+            if (POST) v[0] = alpha * h[base + i] + v[0];
+        }
+        const float y = v[0] * r * (offset + to_f<TW>(w[i]));
+        const float hn = POST ? y : h[base + i] + y;
+        h[base + i] = hn;
+        if (out != nullptr) out[base + i] = from_f<TO>(hn);
+    }
+}
+
+// post != 0: the norm-after-sum form with `alpha`; post == 0: h += norm(a).  out may be null.
+extern "C" int tb_fold_rmsnorm(float* h, int post, float alpha, const void* a, int a_dtype, int n_splits,
+                               long long split_stride, const void* w, int w_dtype, float eps, float offset,
+                               void* out, int out_dtype, int rows, int width, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0) return tb_refuse("fold_rmsnorm: width=%d", width);
+    if (!code_ok(a_dtype) || !code_ok(w_dtype) || !code_ok(out_dtype))
+        return tb_refuse("fold_rmsnorm: unknown dtype codes %d %d %d", a_dtype, w_dtype, out_dtype);
+    if (n_splits < 1) return tb_refuse("fold_rmsnorm: n_splits=%d", n_splits);
+    const int row_cache = (size_t)width * sizeof(float) <= 40 * 1024;
+    const size_t smem = row_cache ? (size_t)width * sizeof(float) : 0;
+    const int threads = norm_threads(width, 1);
+    if (post)
+        DISPATCH3(a_dtype, w_dtype, out_dtype,
+            tb_launch(fold_rmsnorm_kernel<TX, TW, TO, true>, dim3(rows), dim3(threads), smem, stream,
+                h, alpha, (const TX*)a, n_splits, split_stride, (const TW*)w, eps, offset, (TO*)out, width, row_cache));
+    else
+        DISPATCH3(a_dtype, w_dtype, out_dtype,
+            tb_launch(fold_rmsnorm_kernel<TX, TW, TO, false>, dim3(rows), dim3(threads), smem, stream,
+                h, alpha, (const TX*)a, n_splits, split_stride, (const TW*)w, eps, offset, (TO*)out, width, row_cache));
+    return tb_launch_status();
+}
+
+// out = x rounded to the compute dtype (a 32-bit stream read by a 16-bit product).
+template <typename TO>
+__global__ void cast_kernel(const float* __restrict__ x, TO* __restrict__ out, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_f<TO>(x[i]);
+}
+
+extern "C" int tb_cast(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    TB_DISPATCH_1(out_dtype, TO, tb_launch(cast_kernel<TO>, dim3(blocks), dim3(256), 0, stream, x, (TO*)out, (size_t)n));
+    return tb_launch_status();
+}

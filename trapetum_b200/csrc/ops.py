@@ -183,12 +183,54 @@ def residual_add(h: torch.Tensor, a: torch.Tensor) -> None:
            "residual_add")
 
 
+def fold_rmsnorm(h: torch.Tensor, a: torch.Tensor, w: torch.Tensor, eps: float, offset: float,
+                 alpha: Optional[float], out_dtype: Optional[torch.dtype]) -> Optional[torch.Tensor]:
+    """``alpha`` None: h += norm(a); a number: h <- norm(alpha * h + a) (the norm after the sum).  h float32, in
+    place; ``a`` [rows, width] or float32 partial sums [splits, rows, width].  With ``out_dtype`` also returns the new
+    h rounded to that dtype."""
+    _cuda(h, a, w)
+    if h.dtype != torch.float32 or h.dim() != 2 or not h.is_contiguous():
+        raise KernelError("fold_rmsnorm: the residual stream must be contiguous float32 [rows, width]")
+    n_splits, split_stride = 1, 0
+    if a.dim() == 3:
+        if a.dtype != torch.float32:
+            raise KernelError("fold_rmsnorm: partial sums must be float32")
+        n_splits, split_stride = a.shape[0], a.stride(0)
+        if tuple(a.shape[1:]) != tuple(h.shape) or a.stride(1) != h.shape[1] or a.stride(2) != 1:
+            raise KernelError(f"fold_rmsnorm: partial sums {tuple(a.shape)} do not fit the stream {tuple(h.shape)}")
+    elif a.shape != h.shape or not a.is_contiguous():
+        raise KernelError(f"fold_rmsnorm: branch {tuple(a.shape)} does not fit the stream {tuple(h.shape)}")
+    if w.numel() != h.shape[1] or not w.is_contiguous():
+        raise KernelError("fold_rmsnorm: the norm weight does not fit the row width")
+    out = torch.empty(h.shape, dtype=out_dtype, device=h.device) if out_dtype is not None else None
+    lib = build.load("norm")
+    _check(lib, lib.tb_fold_rmsnorm(_ptr(h), c_int(0 if alpha is None else 1), c_float(alpha or 0.0), _ptr(a),
+                                    c_int(code(a.dtype)), c_int(n_splits), c_longlong(split_stride), _ptr(w),
+                                    c_int(code(w.dtype)), c_float(eps), c_float(offset), _ptr(out),
+                                    c_int(code(out_dtype) if out is not None else 0), c_int(h.shape[0]),
+                                    c_int(h.shape[1]), _stream()), "fold_rmsnorm")
+    return out
+
+
+def cast(x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """A float32 tensor rounded to ``out_dtype``."""
+    _cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("cast: wants a contiguous float32 tensor")
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    lib = build.load("norm")
+    _check(lib, lib.tb_cast(_ptr(x), _ptr(out), c_int(code(out_dtype)), c_longlong(x.numel()), _stream()), "cast")
+    return out
+
+
 # ---------------------------------------------------------------------------
-ACTIVATIONS = {"gelu_tanh": 0, "silu": 1}
+ACTIVATIONS = {"gelu_tanh": 0, "silu": 1, "clamped_swish": 2}
+ACTIVATIONS_WITH_LIMIT = ("clamped_swish",)
 
 
-def gated_act(gu: torch.Tensor, activation: str, out_dtype: torch.dtype) -> torch.Tensor:
-    """act(gu[:, :I]) * gu[:, I:]."""
+def gated_act(gu: torch.Tensor, activation: str, out_dtype: torch.dtype, limit: float = 0.0) -> torch.Tensor:
+    """act(gu[:, :I]) * gu[:, I:]; for "clamped_swish" (which takes ``limit`` L):
+    g' = min(g, L), u' = clamp(u, -L, L), g' sigmoid(1.702 g') (u' + 1)."""
     _cuda(gu)
     if gu.dim() != 2 or not gu.is_contiguous() or gu.shape[1] % 2:
         raise KernelError("gated_act: input must be contiguous [rows, 2*intermediate]")
@@ -197,10 +239,37 @@ def gated_act(gu: torch.Tensor, activation: str, out_dtype: torch.dtype) -> torc
     inter = gu.shape[1] // 2
     out = torch.empty((gu.shape[0], inter), dtype=out_dtype, device=gu.device)
     lib = build.load("activation")
-    _check(lib, lib.tb_gated_act(_ptr(gu), c_int(code(gu.dtype)), _ptr(out), c_int(code(out_dtype)),
-                                 c_int(gu.shape[0]), c_int(inter), c_int(ACTIVATIONS[activation]), _stream()),
-           "gated_act")
+    _check(lib, lib.tb_gated_act_limit(_ptr(gu), c_int(code(gu.dtype)), _ptr(out), c_int(code(out_dtype)),
+                                       c_int(gu.shape[0]), c_int(inter), c_int(ACTIVATIONS[activation]),
+                                       c_float(limit), _stream()), "gated_act")
     return out
+
+
+def token_gate(g: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, col0: int) -> torch.Tensor:
+    """out[t, j] = gelu_tanh(g[t, j]) * table[ids[t], col0 + j], in g's dtype (the product 32-bit)."""
+    _cuda(g, ids, table)
+    if g.dim() != 2 or not g.is_contiguous():
+        raise KernelError("token_gate: g must be contiguous [tokens, dim]")
+    if ids.dtype != torch.int32 or ids.numel() != g.shape[0] or not ids.is_contiguous():
+        raise KernelError("token_gate: ids must be contiguous int32 [tokens]")
+    if table.dim() != 2 or table.stride(1) != 1 or col0 < 0 or col0 + g.shape[1] > table.shape[1]:
+        raise KernelError(f"token_gate: columns {col0}..{col0 + g.shape[1]} do not lie in a table of shape {tuple(table.shape)}")
+    out = torch.empty_like(g)
+    lib = build.load("activation")
+    _check(lib, lib.tb_token_gate(_ptr(g), c_int(code(g.dtype)), _ptr(ids), _ptr(table), c_int(code(table.dtype)),
+                                  c_longlong(table.stride(0)), c_int(col0), c_int(table.shape[0]), _ptr(out),
+                                  c_int(g.shape[0]), c_int(g.shape[1]), _stream()), "token_gate")
+    return out
+
+
+def scale_(x: torch.Tensor, s: float) -> torch.Tensor:
+    """x *= s in place (float32)."""
+    _cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("scale_: wants a contiguous float32 tensor")
+    lib = build.load("activation")
+    _check(lib, lib.tb_scale(_ptr(x), c_float(s), c_longlong(x.numel()), _stream()), "scale")
+    return x
 
 
 def add_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
@@ -295,6 +364,118 @@ def rope_kv(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, rot
     a.partial_row_stride = partial.stride(1) if partial is not None else 0
     lib = build.load("rope_kv")
     _check(lib, lib.tb_rope_kv(ctypes.byref(a), c_int(code(qkv.dtype)), c_int(T), _stream()), "rope_kv")
+
+
+class _HeadNormKvArgs(ctypes.Structure):
+    _fields_ = [("partial", c_void_p), ("n_splits", c_int), ("split_stride", c_longlong), ("partial_row_stride", c_longlong),
+                ("out", c_void_p), ("out_row_stride", c_longlong),
+                ("n_heads", c_int), ("n_kv_heads", c_int), ("head_dim", c_int),
+                ("q_unit", c_int), ("k_unit", c_int), ("v_from_k", c_int),
+                ("eps", c_float), ("temp_coef", c_float), ("temp_every", c_int),
+                ("positions", c_void_p), ("token_seq", c_void_p), ("len_after", c_void_p),
+                ("k_pool", c_void_p), ("v_pool", c_void_p), ("page_table", c_void_p), ("pt_stride", c_int),
+                ("page_rows", c_int), ("ring_rows", c_int)]
+
+
+def headnorm_kv(partial: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, out_dtype: torch.dtype,
+                q_unit: bool, k_unit: bool, v_from_k: bool, eps: float, temp_coef: float, temp_every: int,
+                positions: torch.Tensor, token_seq: torch.Tensor, len_after: torch.Tensor,
+                k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], page_table: Optional[torch.Tensor],
+                ring_rows: int) -> torch.Tensor:
+    """From the q/k(/v) product's float32 partial sums [splits, T, width] to [T, (n_heads + 2 n_kv_heads) * head_dim]
+    in ``out_dtype``: q and k heads divided by their root mean square (``q_unit``, ``k_unit``; eps inside the root),
+    q times ``1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)`` (``temp_every`` 0: off), v the product's own
+    v columns or, with ``v_from_k``, its k columns before the norm; k and v are also written to the cache line."""
+    _cuda(partial, positions, token_seq, len_after, k_pool, v_pool, page_table)
+    in_slots = n_heads + n_kv_heads * (1 if v_from_k else 2)
+    if partial.dtype != torch.float32 or partial.dim() != 3 or partial.stride(2) != 1 or partial.shape[2] != in_slots * head_dim:
+        raise KernelError(f"headnorm_kv: wants float32 partial sums [splits, tokens, {in_slots * head_dim}], "
+                          f"got {tuple(partial.shape)} {partial.dtype}")
+    T = partial.shape[1]
+    for name, t in (("positions", positions), ("token_seq", token_seq)):
+        if t.dtype != torch.int32 or t.numel() != T or not t.is_contiguous():
+            raise KernelError(f"headnorm_kv: {name} must be contiguous int32 [{T}]")
+    if k_pool is not None:
+        for p in (k_pool, v_pool):
+            if p is None or p.dtype != out_dtype or not p.is_contiguous() or tuple(p.shape[1:]) != (n_kv_heads, PAGE_ROWS, head_dim):
+                raise KernelError("headnorm_kv: cache pools must be contiguous [pages, n_kv_heads, PAGE_ROWS, head_dim] "
+                                  "of the output's dtype")
+        if page_table is None or page_table.dtype != torch.int32 or page_table.dim() != 2 or page_table.stride(1) != 1:
+            raise KernelError("headnorm_kv: page_table must be int32 [batch, pages]")
+    out = torch.empty((T, (n_heads + 2 * n_kv_heads) * head_dim), dtype=out_dtype, device=partial.device)
+    a = _HeadNormKvArgs()
+    a.partial = partial.data_ptr(); a.n_splits = partial.shape[0]; a.split_stride = partial.stride(0)
+    a.partial_row_stride = partial.stride(1)
+    a.out = out.data_ptr(); a.out_row_stride = out.stride(0)
+    a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.head_dim = head_dim
+    a.q_unit = int(bool(q_unit)); a.k_unit = int(bool(k_unit)); a.v_from_k = int(bool(v_from_k))
+    a.eps = eps; a.temp_coef = temp_coef; a.temp_every = int(temp_every)
+    a.positions = positions.data_ptr(); a.token_seq = token_seq.data_ptr(); a.len_after = len_after.data_ptr()
+    a.k_pool = k_pool.data_ptr() if k_pool is not None else None
+    a.v_pool = v_pool.data_ptr() if k_pool is not None else None
+    a.page_table = page_table.data_ptr() if k_pool is not None else None
+    a.pt_stride = page_table.stride(0) if k_pool is not None else 0
+    a.page_rows = PAGE_ROWS; a.ring_rows = ring_rows
+    lib = build.load("headnorm_kv")
+    _check(lib, lib.tb_headnorm_kv(ctypes.byref(a), c_int(code(out_dtype)), c_int(T), _stream()), "headnorm_kv")
+    return out
+
+
+class _Mamba2Args(ctypes.Structure):
+    _fields_ = [("proj", c_void_p), ("proj_stride", c_longlong),
+                ("heads", c_int), ("P", c_int), ("N", c_int), ("groups", c_int), ("taps", c_int), ("norm_groups", c_int),
+                ("conv_w", c_void_p), ("conv_b", c_void_p), ("dt_bias", c_void_p), ("A_log", c_void_p), ("D", c_void_p),
+                ("norm_w", c_void_p), ("eps", c_float),
+                ("state", c_void_p), ("state_stride", c_longlong),
+                ("seq_start", c_void_p), ("token_seq", c_void_p), ("slot_ids", c_void_p),
+                ("xbc", c_void_p), ("y", c_void_p), ("out", c_void_p), ("batch", c_int), ("n_tokens", c_int)]
+
+
+def mamba2_state_size(heads: int, P: int, N: int, groups: int, taps: int) -> int:
+    """32-bit numbers of one sequence's state: S [heads, P, N], then the last taps-1 conv inputs [taps-1, channels]."""
+    return heads * P * N + (taps - 1) * (heads * P + 2 * groups * N)
+
+
+def mamba2(proj: torch.Tensor, heads: int, P: int, N: int, groups: int, taps: int, norm_groups: int,
+           conv_w: torch.Tensor, conv_b: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor,
+           norm_w: torch.Tensor, eps: float, state: torch.Tensor, seq_start: torch.Tensor, token_seq: torch.Tensor,
+           slot_ids: torch.Tensor, batch: int, one_token_each: bool) -> torch.Tensor:
+    """Everything of the state-space mixer between its two products (see mamba2.cu): from the input product's rows
+    ``proj`` [T, inner + channels + heads] to the gated, normed [T, inner] that the output product reads, with the
+    sequences' states (``state`` [slots, mamba2_state_size] float32, rows picked by ``slot_ids``) carried along."""
+    _cuda(proj, conv_w, conv_b, dt_bias, A_log, D, norm_w, state, seq_start, token_seq, slot_ids)
+    inner, ch = heads * P, heads * P + 2 * groups * N
+    _rows_contig(proj, "mamba2: proj")
+    T = proj.shape[0]
+    if proj.shape[1] != inner + ch + heads:
+        raise KernelError(f"mamba2: the input product has {proj.shape[1]} columns, the sizes ask for {inner + ch + heads}")
+    wd = conv_w.dtype
+    for name, t, shape in (("conv", conv_w, (ch, taps)), ("conv bias", conv_b, (ch,)), ("dt_bias", dt_bias, (heads,)),
+                           ("A_log", A_log, (heads,)), ("D", D, (heads,)), ("norm", norm_w, (inner,))):
+        if tuple(t.shape) != shape or t.dtype != wd or not t.is_contiguous():
+            raise KernelError(f"mamba2: {name} must be contiguous {shape} of dtype {wd}, got {tuple(t.shape)} {t.dtype}")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or \
+            state.shape[1] != mamba2_state_size(heads, P, N, groups, taps):
+        raise KernelError("mamba2: the state must be float32 [slots, mamba2_state_size]")
+    dt = proj.dtype
+    xbc = torch.empty((T, ch), dtype=dt, device=proj.device)
+    y = torch.empty((T, inner), dtype=torch.float32, device=proj.device)
+    out = torch.empty((T, inner), dtype=dt, device=proj.device)
+    a = _Mamba2Args()
+    a.proj = proj.data_ptr(); a.proj_stride = proj.stride(0)
+    a.heads = heads; a.P = P; a.N = N; a.groups = groups; a.taps = taps; a.norm_groups = norm_groups
+    a.conv_w = conv_w.data_ptr(); a.conv_b = conv_b.data_ptr(); a.dt_bias = dt_bias.data_ptr()
+    a.A_log = A_log.data_ptr(); a.D = D.data_ptr(); a.norm_w = norm_w.data_ptr(); a.eps = eps
+    a.state = state.data_ptr(); a.state_stride = state.stride(0)
+    a.seq_start = seq_start.data_ptr(); a.token_seq = token_seq.data_ptr(); a.slot_ids = slot_ids.data_ptr()
+    a.xbc = xbc.data_ptr(); a.y = y.data_ptr(); a.out = out.data_ptr(); a.batch = batch; a.n_tokens = T
+    lib = build.load("mamba2")
+    cd, cw = c_int(code(dt)), c_int(code(wd))
+    _check(lib, lib.tb_mamba2_conv(ctypes.byref(a), cd, cw, c_int(int(bool(one_token_each))), _stream()), "mamba2_conv",
+           1 if one_token_each or taps == 1 else 2)
+    _check(lib, lib.tb_mamba2_scan(ctypes.byref(a), cd, cw, _stream()), "mamba2_scan")
+    _check(lib, lib.tb_mamba2_gate_norm(ctypes.byref(a), cd, cw, _stream()), "mamba2_gate_norm")
+    return out
 
 
 # ---------------------------------------------------------------------------
@@ -447,9 +628,17 @@ def gemm_tc_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+GEMM_TC_GATES = ("gelu_tanh", "silu")
+
+
+def gemm_tc_gates(activation: str) -> bool:
+    """Whether the tensor-core product's epilogue can apply this gated activation itself."""
+    return activation in GEMM_TC_GATES
+
+
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: float = 0.0,
             splits: Optional[int] = None, out: Optional[torch.Tensor] = None, partials: bool = False,
-            gated_act: Optional[str] = None) -> torch.Tensor:
+            gated_act: Optional[str] = None, act_limit: float = 0.0) -> torch.Tensor:
     """a[M,K] @ w[N,K]^T in bfloat16 on tcgen05 tensor cores with 32-bit accumulation.
     ``splits`` None: the library picks the K split (more than 1 only for few tokens and few weight rows).
     ``partials=True`` returns float32 [splits, M, N] whose sum over the first axis, taken in order, is the
@@ -468,8 +657,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: f
         splits = lib.tb_gemm_tc_splits(c_int(M), c_int(N), c_int(K), c_int(sm_count(a.device)))
     splits = int(lib.tb_gemm_tc_effective_splits(c_int(K), c_int(splits)))
     if gated_act is not None:
-        if gated_act not in ACTIVATIONS:
-            raise KernelError(f"gemm_tc: unknown activation '{gated_act}' (known: {sorted(ACTIVATIONS)})")
+        if not gemm_tc_gates(gated_act):
+            raise KernelError(f"gemm_tc: the epilogue does not know activation '{gated_act}' (known: {GEMM_TC_GATES})")
         if N % 32 or partials or softcap:
             raise KernelError("gemm_tc: the gated epilogue needs a multiple of 32 weight rows, no partials, no cap")
         out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)

@@ -185,7 +185,7 @@ class Engine:
                           token_seq=dev["token_seq"], seq_start=dev["seq_start"], len_after=dev["len_after"],
                           slot_ids=dev["slot_ids"], slots=slots, seq_lens=lens, max_seq_len=max(lens),
                           max_len_after=max_after, len_bucket=len_bucket(max_after),
-                          uneven=0 if is_prefill else unevenness(after))
+                          uneven=0 if is_prefill else unevenness(after), token_ids=dev["ids"])
         n_want = arrays["want"].size
         if n_want == 0:
             # nothing is asked for: the layers still run (they fill the cache), the head does not
@@ -306,4 +306,4 @@ class _DecodeShape:
         return StepContext(is_prefill=False, n_tokens=self.B, batch=self.B, positions=d["positions"],
                            token_seq=d["token_seq"], seq_start=d["seq_start"], len_after=d["len_after"],
                            slot_ids=d["slot_ids"], slots=list(slots), seq_lens=[1] * self.B, max_seq_len=1,
-                           max_len_after=max_after, len_bucket=self.bucket, uneven=self.uneven)
+                           max_len_after=max_after, len_bucket=self.bucket, uneven=self.uneven, token_ids=d["ids"])

@@ -2,7 +2,7 @@
 from .base import (Block, FeedForward, KVNeed, Mixer, Norm, Part, PositionEncoding, Runtime, StateNeed,
                    build_part, known_parts, register_part)
 from .stream import ResidualStream
-from . import norm, rope, attention, feed_forward, block, ends  # noqa: F401  (register the built-in kinds)
+from . import norm, rope, attention, mamba2, feed_forward, block, ends  # noqa: F401  (register the built-in kinds)
 
 __all__ = ["Block", "FeedForward", "KVNeed", "Mixer", "Norm", "Part", "PositionEncoding", "Runtime", "StateNeed",
            "ResidualStream", "build_part", "known_parts", "register_part"]

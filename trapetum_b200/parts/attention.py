@@ -21,6 +21,17 @@ own, so such a mixer is a matter of parameters, not of a change to a kernel.
 The reference fixes ``scale = rsqrt(head_dim)`` (codebook_gemv.cu:250) and has
 no window (runtime/src/lib.rs:4455).
 
+Three more options serve mixers whose positions do not enter through a rotation
+(``position`` of kind "none"); they run in one kernel between the projection and
+the attention kernel (``ops.headnorm_kv``), all in 32-bit:
+
+* ``v`` None: the values are the keys as projected (no v matrix; the cache still
+  keeps keys and values, because the keys may be normed and the values are not);
+* ``head_unit_norm`` ``{"q": bool, "k": bool, "eps": e}``: every query / key head is
+  divided by its root mean square over ``head_dim`` (no weight);
+* ``q_temp`` ``{"coef": c, "every": n}``: the query at position p is multiplied by
+  ``1 + c * ln(floor((p + 1) / n) + 1)``.
+
 The three projections are fused into one matrix when the weights are bound, so
 a step runs one product for q, k and v.
 """
@@ -64,14 +75,28 @@ class Attention(Mixer):
         self.k_norm = build_part("norm", p["k_norm"], prefix, rt) if p.get("k_norm") else None
         self.b_qkv: Optional[torch.Tensor] = None
         self.b_o: Optional[torch.Tensor] = None
+        self.v_from_k = p.get("v", "") is None
+        unit = p.get("head_unit_norm") or {}
+        self.q_unit, self.k_unit = bool(unit.get("q")), bool(unit.get("k"))
+        self.unit_eps = float(unit.get("eps", 0.0))
+        temp = p.get("q_temp") or {}
+        self.temp_coef = float(temp.get("coef", 0.0))
+        self.temp_every = int(temp.get("every", 0)) if self.temp_coef else 0
+        if temp and self.temp_coef and self.temp_every < 1:
+            raise ValueError(f"attention: q_temp 'every' must be at least 1, got {temp.get('every')!r}")
+        self.prepared = self.v_from_k or self.q_unit or self.k_unit or self.temp_every > 0
+        if self.prepared and (self.position.rotary_table() != (None, 0) or self.bias_names or self.q_norm or self.k_norm):
+            raise ValueError("attention: 'v' None, 'head_unit_norm' and 'q_temp' go with position 'none' and without "
+                             "biases or weighted head norms")
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         specs = {
             self._name("q"): TensorSpec((self.qd, self.hidden)),
             self._name("k"): TensorSpec((self.kvd, self.hidden)),
-            self._name("v"): TensorSpec((self.kvd, self.hidden)),
             self._name("o"): TensorSpec((self.hidden, self.qd)),
         }
+        if not self.v_from_k:
+            specs[self._name("v")] = TensorSpec((self.kvd, self.hidden))
         sizes = {"q": self.qd, "k": self.kvd, "v": self.kvd, "o": self.hidden}
         for key, name in self.bias_names.items():
             specs[self.prefix + name] = TensorSpec((sizes[key],))
@@ -81,9 +106,10 @@ class Attention(Mixer):
         return specs
 
     def bind(self, tensors) -> None:
-        q, k, v = (tensors[self._name(n)] for n in ("q", "k", "v"))
-        dt = q.dtype if (q.dtype == k.dtype == v.dtype) else torch.float32
-        self.w_qkv = torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0).contiguous()
+        mats = [tensors[self._name(n)] for n in (("q", "k") if self.v_from_k else ("q", "k", "v"))]
+        q = mats[0]
+        dt = q.dtype if all(m.dtype == q.dtype for m in mats) else torch.float32
+        self.w_qkv = torch.cat([m.to(dt) for m in mats], dim=0).contiguous()
         self.w_o = tensors[self._name("o")]
         self.position.bind(tensors)
         if any(key in self.bias_names for key in "qkv"):
@@ -123,6 +149,8 @@ class Attention(Mixer):
 
     def kernel_files(self):
         fast = ("attention_decode",) if ops.attn_decode_takes(self.rt.dtype, self.n_heads, self.n_kv, self.hd) else ()
+        if self.prepared:
+            fast += ("headnorm_kv",)
         if self.bias_names:
             fast += ("activation",)
         for n in (self.q_norm, self.k_norm):
@@ -139,6 +167,8 @@ class Attention(Mixer):
 
     def forward(self, x, ctx, line):
         dt = self.rt.dtype
+        if self.prepared:
+            return self._forward_prepared(x, ctx, line)
         if line.owner:
             plain = self.b_qkv is None and self.q_norm is None and self.k_norm is None
             if plain and dt == torch.bfloat16 and x.shape[0] <= 128 and ops.gemm_tc_takes(x, self.w_qkv):
@@ -168,6 +198,29 @@ class Attention(Mixer):
             self._finish_projection(q, self.n_heads, 0)
             self.position.rotate_and_store(q, self.n_heads, 0, ctx, line, store=False)
             k, v = ctx.step_kv[line.entry] if ctx.is_prefill else (None, None)
+        if ctx.is_prefill:
+            o = ops.attn_prefill(q, k, v, ctx.seq_start, ctx.token_seq, self.n_heads, self.n_kv, self.hd,
+                                 self.scale, self.softcap, self.window or 0, ctx.max_seq_len, ctx.seq_lens, ctx.memo)
+        else:
+            o = ops.attn_decode(q, line.k, line.v, line.page_table, ctx.len_after, self.n_heads, self.n_kv,
+                                self.hd, self.scale, self.softcap, self.window or 0, line.ring_rows, ctx.len_bucket,
+                                ctx.uneven)
+        return self._out(o)
+
+
+    def _forward_prepared(self, x, ctx, line):
+        """The path of ``v`` None / ``head_unit_norm`` / ``q_temp``: the projection as 32-bit partial sums, one kernel
+        that norms, scales, rounds and fills the cache, then the same attention kernels as every other mixer."""
+        dt = self.rt.dtype
+        if not line.owner:
+            raise NotImplementedError("attention: a prepared mixer that reads another call's cache is not built")
+        part = linear_partials(x, self.w_qkv)
+        qkv = ops.headnorm_kv(part, self.n_heads, self.n_kv, self.hd, dt, self.q_unit, self.k_unit, self.v_from_k,
+                              self.unit_eps, self.temp_coef, self.temp_every, ctx.positions, ctx.token_seq,
+                              ctx.len_after, line.k, line.v, line.page_table, line.ring_rows)
+        q = qkv[:, :self.qd]
+        k = qkv[:, self.qd:self.qd + self.kvd]
+        v = qkv[:, self.qd + self.kvd:]
         if ctx.is_prefill:
             o = ops.attn_prefill(q, k, v, ctx.seq_start, ctx.token_seq, self.n_heads, self.n_kv, self.hd,
                                  self.scale, self.softcap, self.window or 0, ctx.max_seq_len, ctx.seq_lens, ctx.memo)

@@ -102,6 +102,13 @@ class Norm(Part):
         return then.apply(h, out_dtype) if then is not None else None
 
 
+    def fold(self, h: torch.Tensor, a: torch.Tensor, alpha: Optional[float], out_dtype) -> Optional[torch.Tensor]:
+        """``alpha`` None: ``h += self(a)``; a number: ``h <- self(alpha * h + a)`` (the norm after the sum); in
+        place.  With ``out_dtype`` also returns the new ``h`` rounded to it.  A norm that an arrangement with the norm
+        after the sum uses has to offer this."""
+        raise NotImplementedError(f"{type(self).__name__} has no form that norms after the sum")
+
+
 class PositionEncoding(Part):
     def rotary_table(self):
         """``(inv_freq, rotary_dim)`` if this encoding is the rotate-half rotation of the first ``rotary_dim`` dims

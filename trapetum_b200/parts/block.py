@@ -10,6 +10,15 @@
 
     h += mixer(pre_mixer_norm(h));  h += feed_forward(pre_ffn_norm(h))
 
+``post_norm``: the norm comes after the sum, the stream is scaled by ``alpha`` on
+the way in, and both sublayers read the stream itself:
+
+    h <- mixer_norm(alpha h + mixer(h));  h <- ffn_norm(alpha h + feed_forward(h))
+
+(the second line only if the layer has a feed-forward), then, if the layer has a
+``side`` input (a feed-forward that may look at the step's token ids),
+``h <- h + side_norm(side(h))``.
+
 A block only talks to the :class:`~trapetum_b200.parts.stream.ResidualStream`,
 which decides how additions and norms are fused.
 """
@@ -71,5 +80,40 @@ class PreNormBlock(_NormedBlock):
         stream.add(self.feed_forward.forward(x, ctx))
 
 
+class PostNormBlock(_NormedBlock):
+    """Parameters: ``alpha``, ``mixer_norm``, ``ffn_norm`` (None when the layer's feed-forward is of kind "none"),
+    ``side`` (a feed-forward spec or None) and ``side_norm``."""
+
+    def __init__(self, params, prefix, rt, mixer, feed_forward):
+        Block.__init__(self, params, prefix, rt, mixer, feed_forward)
+        self.alpha = float(params["alpha"])
+        self.has_ffn = not getattr(feed_forward, "absent", False)
+        self.norms = {"mixer_norm": build_part("norm", params["mixer_norm"], prefix, rt)}
+        if self.has_ffn:
+            if not params.get("ffn_norm"):
+                raise ValueError("post_norm: a layer with a feed-forward needs 'ffn_norm'")
+            self.norms["ffn_norm"] = build_part("norm", params["ffn_norm"], prefix, rt)
+        self.side = None
+        if params.get("side"):
+            self.side = build_part("feed_forward", params["side"], prefix, rt)
+            self.norms["side_norm"] = build_part("norm", params["side_norm"], prefix, rt)
+
+    @property
+    def graph_safe(self):
+        return self.side is None or getattr(self.side, "graph_safe", False)
+
+    def parts(self):
+        return list(self.norms.values()) + [self.mixer, self.feed_forward] + ([self.side] if self.side else [])
+
+    def forward(self, stream, ctx, cache) -> None:
+        dt = self.rt.dtype
+        stream.fold_normed(self.mixer.forward(stream.read(dt), ctx, cache), self.norms["mixer_norm"], self.alpha)
+        if self.has_ffn:
+            stream.fold_normed(self.feed_forward.forward(stream.read(dt), ctx), self.norms["ffn_norm"], self.alpha)
+        if self.side is not None:
+            stream.add_normed(self.side.forward(stream.read(dt), ctx), self.norms["side_norm"])
+
+
+register_part("block", "post_norm", PostNormBlock)
 register_part("block", "sandwich", SandwichBlock)
 register_part("block", "pre_norm", PreNormBlock)

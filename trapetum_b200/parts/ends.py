@@ -47,6 +47,9 @@ class LinearHead(Part):
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
         self.softcap = float(params["softcap"]) if params.get("softcap") else 0.0
+        self.scale = float(params["scale"]) if params.get("scale") is not None else 1.0      # logits = (x W^T) * scale
+        if self.scale != 1.0 and self.softcap:
+            raise ValueError("linear_head: a scale and a soft cap together are not defined")
         self.tied_to = params.get("tied_to")
         self.weight: Optional[torch.Tensor] = None
 
@@ -61,10 +64,11 @@ class LinearHead(Part):
         self.weight = own if own is not None else tensors[self.prefix + self.tied_to]
 
     def kernel_files(self):
-        return linear_kernels(self.rt.dtype)
+        return linear_kernels(self.rt.dtype) + (("activation",) if self.scale != 1.0 else ())
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return linear(x, self.weight, torch.float32, self.softcap)
+        logits = linear(x, self.weight, torch.float32, self.softcap)
+        return ops.scale_(logits, self.scale) if self.scale != 1.0 else logits
 
 
 register_part("embedding", "embedding", Embedding)

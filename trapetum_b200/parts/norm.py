@@ -25,7 +25,8 @@ class RMSNorm(Norm):
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {self._name("weight"): TensorSpec((self.size,), "norm")}
+        # "norm": drawn around 0 in random mode (the (1 + w) form); "gain": around 1 (a plain weight)
+        return {self._name("weight"): TensorSpec((self.size,), self.params.get("role", "norm"))}
 
     def bind(self, tensors) -> None:
         self.weight = tensors[self._name("weight")]
@@ -44,6 +45,10 @@ class RMSNorm(Norm):
                                    then.weight, then.eps, then.offset, out_dtype)
         ops.add_rmsnorm(h, a, self.weight, self.eps, self.offset)
         return then.apply(h, out_dtype)
+
+
+    def fold(self, h, a, alpha, out_dtype):
+        return ops.fold_rmsnorm(h, a if a.dim() == 3 else a.contiguous(), self.weight, self.eps, self.offset, alpha, out_dtype)
 
 
 register_part("norm", "rmsnorm", RMSNorm)

@@ -6,6 +6,11 @@ Blocks never add into the stream themselves.  They call :meth:`add` or
 next normalised input; the stream holds an addition back until the next read
 so that ``h += norm_a(a); x = norm_b(h)`` runs as one kernel, also across the
 border between two layers.  The sum itself is always 32-bit.
+
+Arrangements that norm AFTER the sum replace the stream instead of adding to it:
+:meth:`fold_normed` is ``h <- norm(alpha * h + a)``, and their sublayers read the
+stream itself through :meth:`read` (a copy in the compute dtype when that is not
+32-bit), which rides along with whatever was still waiting.
 """
 from __future__ import annotations
 
@@ -21,27 +26,45 @@ class ResidualStream:
     def __init__(self, h: torch.Tensor):
         assert h.dtype == torch.float32
         self.h = h
-        self._pending = None          # (branch output, its norm or None)
+        self._pending = None          # (branch output, its norm or None, alpha or None)
 
     def add(self, a: torch.Tensor) -> None:
         """h += a (no norm on the branch output)."""
         self._flush()
-        self._pending = (a, None)
+        self._pending = (a, None, None)
 
     def add_normed(self, a: torch.Tensor, norm: Norm) -> None:
         """h += norm(a)."""
         self._flush()
-        self._pending = (a, norm)
+        self._pending = (a, norm, None)
+
+    def fold_normed(self, a: torch.Tensor, norm: Norm, alpha: float) -> None:
+        """h <- norm(alpha * h + a): the norm after the sum."""
+        self._flush()
+        self._pending = (a, norm, float(alpha))
 
     def normed(self, norm: Norm, out_dtype: torch.dtype) -> torch.Tensor:
         """norm(h), after whatever addition was still waiting."""
-        if self._pending is not None:
-            a, post = self._pending
+        if self._pending is not None and self._pending[2] is None:
+            a, post, _ = self._pending
             self._pending = None
             if post is not None:
                 return post.add_to(self.h, a, norm, out_dtype)
             ops.residual_add(self.h, a)
+        self._flush()
         return norm.apply(self.h, out_dtype)
+
+    def read(self, out_dtype: torch.dtype) -> torch.Tensor:
+        """The stream itself for a sublayer that reads it unnormed: ``h`` when the compute dtype is 32-bit, else a
+        rounded copy, made by the kernel that applies what was still waiting."""
+        want = None if out_dtype == torch.float32 else out_dtype
+        if self._pending is not None and self._pending[1] is not None:
+            a, norm, alpha = self._pending
+            self._pending = None
+            out = norm.fold(self.h, a, alpha, want)
+            return self.h if want is None else out
+        self._flush()
+        return self.h if want is None else ops.cast(self.h, want)
 
     def value(self) -> torch.Tensor:
         self._flush()
@@ -50,9 +73,11 @@ class ResidualStream:
     def _flush(self) -> None:
         if self._pending is None:
             return
-        a, post = self._pending
+        a, post, alpha = self._pending
         self._pending = None
-        if post is not None:
+        if alpha is not None:
+            post.fold(self.h, a, alpha, None)
+        elif post is not None:
             post.add_to(self.h, a, None, None)
         else:
             ops.residual_add(self.h, a)

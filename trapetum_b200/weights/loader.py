@@ -59,7 +59,7 @@ class TensorSpec:
     """What a part expects of one tensor.
 
     role: ``"matrix"`` and ``"embedding"`` are drawn N(0, std) in random mode,
-    ``"norm"`` N(0, norm_std); ``"table"`` is an integer table (zeros in random
+    ``"norm"`` N(0, norm_std), ``"gain"`` 1 + N(0, norm_std); ``"table"`` is an integer table (zeros in random
     mode).  ``optional`` tensors may be absent (the part then falls back, for
     instance a tied output head)."""
     shape: Tuple[int, ...]
@@ -143,9 +143,12 @@ def random_tensors(wanted: Dict[str, TensorSpec], seed: int, std: float, norm_st
         if spec.role == "table":
             yield name, torch.zeros(spec.shape, dtype=torch.int32, device=device)
             continue
-        dt = norm_dtype if (spec.role == "norm" and norm_dtype is not None) else dtype
+        dt = norm_dtype if (spec.role in ("norm", "gain") and norm_dtype is not None) else dtype
         t = torch.empty(spec.shape, dtype=dt, device=device)
-        yield name, fill_normal(t, seed, name, norm_std if spec.role == "norm" else std)
+        fill_normal(t, seed, name, norm_std if spec.role in ("norm", "gain") else std)
+        if spec.role == "gain":
+            t += 1.0          # torch rounds the sum to the tensor's dtype
+        yield name, t
 
 
 def write_random_model(folder: str, config: dict, seed: int, std: float = 0.02, norm_std: float = 0.1,
@@ -170,7 +173,7 @@ def write_random_model(folder: str, config: dict, seed: int, std: float = 0.02, 
         if spec.optional:
             continue
         dt = torch.int32 if spec.role == "table" else \
-            (norm_dtype if (spec.role == "norm" and norm_dtype is not None) else torch.bfloat16)
+            (norm_dtype if (spec.role in ("norm", "gain") and norm_dtype is not None) else torch.bfloat16)
         layout.append((name, dt, tuple(spec.shape)))
     write_safetensors(os.path.join(folder, "model.safetensors"),
                       random_tensors(wanted, seed, std, norm_std, device=device, norm_dtype=norm_dtype),
