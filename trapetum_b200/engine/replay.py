@@ -14,10 +14,18 @@ import numpy as np
 
 
 
+# ``max_tokens`` counts the tokens that live requests hold, not the empty rows of each request's last page:
+# room for that padding of up to this many live requests is added.
+PADDING_PAGES = 16
+MAX_LIVE = 256          # slots; a per-sequence state of a recurrent mixer is kept for each
+
+
 class Replayer:
     def __init__(self, model_dir: str, dtype: str, max_tokens: int, device: str = "cuda:0", host=None):
         import trapetum_b200 as tb
-        self.engine = tb.Engine(tb.load_model(model_dir, dtype, device, host=host), max_tokens)
+        from ..csrc.ops import PAGE_ROWS
+        self.engine = tb.Engine(tb.load_model(model_dir, dtype, device, host=host),
+                                max_tokens + PADDING_PAGES * PAGE_ROWS, max_slots=MAX_LIVE)
         self.slot_of: Dict[str, int] = {}
 
     def run_step(self, rec: dict) -> Optional[np.ndarray]:
