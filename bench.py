@@ -18,6 +18,14 @@ Weights are made on the device by the counter-based generator (``tb.random_model
 MEASURED_PEAKS.json beside this file when the driver wrote it, otherwise from the fallback figures
 (6.65 TB/s, 1.59 PFLOP/s).
 
+    python bench.py --design divanex [--sizes small,medium,large] [--batch 8] [--context 2048]
+
+``--design divanex`` is a measurement of its own (the default workload and its line stay as they are): Divanex
+models with random weights at a few layer sizes, a 2,048-token prompt and decode steps of ``batch`` sequences
+at ``context`` tokens, each beside a Gemma-2 model of the same width, depth, head counts, head size, feed-forward
+width and vocabulary on the same host, and the design's own kernels timed alone beside the like kernels of
+Gemma-2, each with its fraction of its roofline.
+
 This library runs on one GPU: for --gpus > 1 it says so and exits with 2.
 """
 import argparse
@@ -127,6 +135,176 @@ class ClockSampler:
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None,
                 "sm_max_mhz": int(self.rows[0][1]) if self.rows[0][1].isdigit() else None, "reasons": reasons,
                 "samples": len(self.rows)}
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# --design divanex: the design at sizes that resemble real layers, beside Gemma-2 at equal size
+# ---------------------------------------------------------------------------------------------------------------
+# name -> (width, layers, heads, kv heads, head size, ff, state-space heads, their head size, state, vocabulary)
+DESIGN_SIZES = {"small": (1024, 12, 8, 2, 128, 4096, 32, 64, 64, 32768),
+                "medium": (2048, 16, 16, 4, 128, 8192, 64, 64, 128, 65536),
+                "large": (4096, 16, 32, 8, 128, 14336, 128, 64, 128, 131072)}
+FP32_TFLOPS_NOMINAL = 72.0      # 148 SMs x 128 FMA x 2 x 1.9 GHz: the bound of 32-bit arithmetic outside the tensor cores
+
+
+def divanex_config(size):
+    W, L, H, G, d, ff, mh, mp, N, V = DESIGN_SIZES[size]
+    attn = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "softcap": 30.0,
+                                           "q_temp": {"coef": 0.5, "every": 64}},
+            "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}}
+    ssm = {"type": "mamba2", "mixer": {"heads": mh, "vdim": mp, "state": N, "groups": 1, "conv": 4, "norm_groups": 1}, "mlp": None}
+    return {"architecture": "Divanex", "vocab": V, "width": W, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "postln_alpha": 2.0, "logit_scale": 0.25, "token_side": {"dim": 64},
+            "layers": [attn if i % 2 == 0 else ssm for i in range(L)]}
+
+
+def gemma_like(size):
+    W, L, H, G, d, ff, mh, mp, N, V = DESIGN_SIZES[size]
+    return dict(_shape(L, W, H, G, d, ff, d), vocab_size=V, sliding_window=4096)
+
+
+def divanex_bytes_flops(cfg, tokens, ctx, batch):
+    """(weight bytes a decode step reads, cache and state bytes per sequence at ``ctx`` tokens, tensor-core FLOPs and
+    32-bit recurrence FLOPs of one ``tokens``-token prompt)."""
+    W, V = cfg["width"], cfg["vocab"]
+    wb, cb, fl, rf = V * W + W, 0, 2 * V * W, 0
+    sd = cfg["token_side"]["dim"]
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        per = 2 * sd * W + 2 * W                                    # side gate and proj, norms
+        if L["type"] == "attention":
+            qd, kvd = m["heads"] * m["dim"], m["kv_heads"] * m["dim"]
+            per += (qd + kvd) * W + W * qd
+            cb += 2 * kvd * ctx * 2
+            fl += 4 * qd * tokens * (tokens + 1) // 2
+        else:
+            inner = m["heads"] * m["vdim"]
+            ch = inner + 2 * m["groups"] * m["state"]
+            per += (inner + ch + m["heads"]) * W + W * inner + ch * m["conv"]
+            cb += 2 * 4 * (inner * m["state"] + (m["conv"] - 1) * ch)      # the state is read and written, 32-bit
+            rf += tokens * inner * m["state"] * 5
+        if L["mlp"]:
+            per += 3 * L["mlp"]["ff"] * W
+        wb += per
+        fl += 2 * tokens * per
+    return 2 * wb, cb, fl, rf
+
+
+def _median_us(torch, fn, flush, reps=15, warm=3):
+    for _ in range(warm):
+        fn()
+    ts = []
+    for _ in range(reps):
+        flush.zero_()                                               # a buffer larger than L2 between timed launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); fn(); e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3)
+    return sorted(ts)[len(ts) // 2]
+
+
+def design_kernels(torch, size, hbm_gbs, tokens=PREFILL_TOKENS):
+    """The design's own kernels alone at ``tokens`` tokens of one prompt, each beside the like kernel of Gemma-2:
+    microseconds, algorithmic bytes (or FLOPs) and the fraction of the roofline."""
+    from trapetum_b200.csrc import ops
+    W, _, H, G, d, ff, mh, mp, N, _ = DESIGN_SIZES[size]
+    dev, bf = "cuda:0", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    T = tokens
+    out = {}
+
+    def rec(name, us, nbytes, flops=0.0, like=None):
+        t_mem, t_fl = nbytes / (hbm_gbs * 1e9) * 1e6, flops / (FP32_TFLOPS_NOMINAL * 1e12) * 1e6
+        out[name] = {"us": round(us, 1), "bytes": int(nbytes), "roofline_us": round(max(t_mem, t_fl), 1),
+                     "frac": round(max(t_mem, t_fl) / us, 3), "bound": "fp32" if t_fl > t_mem else "hbm"}
+        if like:
+            out[name]["like"] = like
+    pos = torch.arange(T, device=dev).int()
+    tseq = torch.zeros(T, device=dev).int()
+    la = torch.tensor([T], device=dev).int()
+    pages = (T + 63) // 64
+    kp = torch.zeros(pages, G, 64, d, dtype=bf, device=dev)
+    vp = torch.zeros_like(kp)
+    table = torch.arange(pages, device=dev).int().view(1, pages)
+    part = torch.randn(1, T, (H + G) * d, device=dev)
+    rec("headnorm_kv", _median_us(torch, lambda: ops.headnorm_kv(part, H, G, d, bf, True, True, True, 1e-5, 0.5, 64, pos, tseq, la, kp, vp, table, 0), flush),
+        part.numel() * 4 + T * (H + 2 * G) * d * 2 + T * 2 * G * d * 2, like="rope_kv")
+    qkv = torch.randn(T, (H + 2 * G) * d, device=dev).to(bf)
+    inv = torch.rand(d // 2, device=dev)
+    rec("rope_kv", _median_us(torch, lambda: ops.rope_kv(qkv, H, G, d, d, inv, pos, tseq, la, kp, vp, table, 0), flush),
+        T * (H + 2 * G) * d * 2 * 2 + T * 2 * G * d * 2)
+    h = torch.randn(T, W, device=dev)
+    a = torch.randn(1, T, W, device=dev)
+    w = torch.ones(W, device=dev).to(bf)
+    rec("fold_rmsnorm", _median_us(torch, lambda: ops.fold_rmsnorm(h, a, w, 1e-5, 0.0, 2.0, bf), flush), T * W * 14, like="add_rmsnorm")
+    rec("add_rmsnorm", _median_us(torch, lambda: ops.add_rmsnorm(h, a, w, 1e-5, 0.0, w, 1e-5, 0.0, bf), flush), T * W * 14)
+    inner, ch = mh * mp, mh * mp + 2 * N
+    proj = torch.randn(T, inner + ch, device=dev).to(bf)
+    dtr = torch.randn(T, mh, device=dev)
+    f32 = lambda *s: torch.randn(*s, device=dev)
+    cw, cb, dtb, Al, D, nw = f32(ch, 4) * .3, f32(ch) * .1, f32(mh) - 1, f32(mh) * .5, f32(mh), f32(inner)
+    state = torch.zeros(1, ops.mamba2_state_size(mh, mp, N, 1, 4), device=dev)
+    ss = torch.tensor([0, T], device=dev).int()
+    slots = torch.zeros(1, device=dev).int()
+    # conv + recurrence + gated norm together (three launches, four with the state's update): bytes of the rows
+    # they read and write once, FLOPs of the recurrence (5 per state element and token, 32-bit)
+    rec("mamba2 (conv, scan, gated norm)",
+        _median_us(torch, lambda: ops.mamba2(proj, dtr, mh, mp, N, 1, 4, 1, cw, cb, dtb, Al, D, nw, 1e-5, state, ss, tseq, slots, 1, False), flush),
+        T * (ch * 2 * 3 + inner * 2 + inner * 4 * 2 + inner * 2), flops=T * inner * N * 5.0, like="attention (prefill)")
+    return out
+
+
+def design_compare(args, torch):
+    """Prints one JSON line: per size, Divanex and the Gemma-2 model of equal size (prefill of one 2,048-token prompt,
+    decode at ``batch`` x ``context``), with bytes, FLOPs and roofline fractions, and the kernels alone."""
+    import trapetum_b200 as tb
+    from trapetum_b200.csrc import ops
+    hbm_gbs, bf16_tflops, peak_src = peaks()
+    warmup = max(3, args.warmup)
+    ctx, batch = args.context, args.batch
+    sizes = [s for s in args.sizes.split(",") if s in DESIGN_SIZES]
+    out = {"design": "divanex", "sizes": {}, "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops, "source": peak_src,
+                                                         "fp32_tflops_nominal": FP32_TFLOPS_NOMINAL},
+           "dtype": "bf16", "data": "synthetic (random weights, random token ids)", "batch": batch, "context": ctx,
+           "timing": "CUDA events; decode: median of five regions of --steps steps; kernels alone: a 256 MB buffer is written "
+                     "between timed launches (larger than L2)"}
+    clocks = ClockSampler()
+    clocks.__enter__()
+    for size in sizes:
+        row = {}
+        for which in ("divanex", "gemma2"):
+            cfg = divanex_config(size) if which == "divanex" else gemma_like(size)
+            V = cfg["vocab"] if which == "divanex" else cfg["vocab_size"]
+            model = tb.random_model(cfg, 7, 0.02, 0.1, "bfloat16", "cuda:0", host="python")
+            engine = tb.Engine(model, max_tokens=batch * (ctx + 64), max_slots=batch)
+            random_cache(engine)
+            pms, hms, wms = time_prefill(engine, torch, PREFILL_TOKENS, V, reps=5, warmup=warmup)
+            r = time_decode(engine, torch, [ctx] * batch, args.steps, warmup, V, clocks=clocks)
+            if which == "divanex":
+                wb, cb, fl, rf = divanex_bytes_flops(cfg, PREFILL_TOKENS, ctx, batch)
+                nbytes = wb + batch * cb
+                pre_ideal = fl / (bf16_tflops * 1e12) + rf / (FP32_TFLOPS_NOMINAL * 1e12)
+            else:
+                nbytes = weight_bytes(cfg) + batch * cache_bytes(cfg, ctx)
+                fl, rf = prefill_flops(cfg, PREFILL_TOKENS), 0
+                pre_ideal = fl / (bf16_tflops * 1e12)
+            row[which] = {
+                "prefill": {"tokens": PREFILL_TOKENS, "ms": round(pms, 3), "tok_s": round(PREFILL_TOKENS * 1e3 / pms, 1),
+                            "tensor_flops": fl, "fp32_recurrence_flops": rf, "frac_of_roofline": round(pre_ideal * 1e3 / pms, 4)},
+                "decode": {"ms": r["ms"], "tok_s": round(batch * 1e3 / r["ms"], 1), "bytes": nbytes,
+                           "gbs": round(nbytes / (r["ms"] * 1e-3) / 1e9, 1),
+                           "frac_of_hbm": round(nbytes / (r["ms"] * 1e-3) / 1e9 / hbm_gbs, 4), "launches": r["launches"]},
+            }
+            engine.check_kernels()
+            del engine, model
+            torch.cuda.empty_cache()
+        row["kernels_alone"] = design_kernels(torch, size, hbm_gbs)
+        out["sizes"][size] = row
+    clocks.__exit__()
+    out["clocks"] = clocks.summary()
+    out["kernel_errors"] = ops.kernel_errors()
+    print(json.dumps(out))
+    return 0
 
 
 HOST = None              # which host runs the models (None: the library's default, the native host for these models)
@@ -477,6 +655,9 @@ def main() -> int:
     ap.add_argument("--leave-out", action="store_true",
                     help="instead of the bench line: the decode step re-timed with one kind of launch left out at a "
                          "time (its results are then wrong; only its time is of interest), one line per kind")
+    ap.add_argument("--design", default=None, choices=["divanex"],
+                    help="instead of the bench line: this design at the layer sizes of --sizes beside Gemma-2 at equal size")
+    ap.add_argument("--sizes", default="small,medium,large", help="with --design: which of small, medium, large")
     ap.add_argument("--gemm-compare", type=int, default=0, metavar="TOKENS",
                     help="instead of the bench line: the four products of a layer of --model at TOKENS tokens, this "
                          "library's kernel beside torch.matmul, one line per product (a comparison only)")
@@ -494,6 +675,10 @@ def main() -> int:
     warmup = max(3, args.warmup)
 
     import torch
+    if args.design:
+        if args.context == 8192:
+            args.context = 2048
+        return design_compare(args, torch)
     if args.gemm_compare:
         return gemm_compare(MODELS[args.model], torch, args.gemm_compare, peaks()[1])
     from trapetum_b200 import Engine

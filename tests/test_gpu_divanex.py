@@ -16,7 +16,7 @@ import plain_divanex as plain
 import trapetum_b200 as tb
 from conftest import ROOT, within
 from divanex_util import (CFG_A, CFG_B, CFG_C, CONFIGS, TOL32, attn, config, dense, logit_error, prompts, random_weights,
-                          ssm, tolerance, write_folder)
+                          ssm, tolerance, worst_ratio, write_folder)
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -46,7 +46,8 @@ def model_of(folders, name, dtype):
 
 
 def close(got, want, tol, what, dtype):
-    within(logit_error(got, want), tol, dtype, what)
+    """``tol``: the tolerances of the positions that ``got`` and ``want`` hold (a tensor), or one number."""
+    within(worst_ratio(got, want, tol), 1.0, dtype, what + " (error / tolerance)")
 
 
 # =================================================================================================================
@@ -135,7 +136,7 @@ def test_state_space_mixer_between_its_products(heads, P, N, groups, taps, ngrou
         T = sum(step_lens)
         seq_start = torch.tensor([0] + list(np.cumsum(step_lens))).int().to(DEV)
         token_seq = torch.repeat_interleave(torch.arange(len(step_lens)), torch.tensor(step_lens)).int().to(DEV)
-        return ops.mamba2(rows.to(DEV).to(dt), heads, P, N, groups, taps, ngroups, dev["conv"], dev["conv.b"], dev["dt_bias"],
+        return ops.mamba2(rows[:, :inner + ch].to(DEV).to(dt), rows[:, inner + ch:].to(DEV).contiguous(), heads, P, N, groups, taps, ngroups, dev["conv"], dev["conv.b"], dev["dt_bias"],
                           dev["A_log"], dev["D"], dev["norm"], eps, state, seq_start, token_seq, slots.to(DEV), len(step_lens),
                           one_each)
 
@@ -143,8 +144,8 @@ def test_state_space_mixer_between_its_products(heads, P, N, groups, taps, ngrou
     for step in range(4):
         step_lens = lens if step == 0 else [1] * len(lens)
         rows = rn(sum(step_lens), inner + ch + heads)
-        if dtype == "bfloat16":
-            rows = rows.to(torch.bfloat16).float()
+        if dtype == "bfloat16":                              # the step sizes stay 32-bit
+            rows[:, :inner + ch] = rows[:, :inner + ch].to(torch.bfloat16).float()
         got = run(rows, step_lens, step > 0).double().cpu()
         at = 0
         for b, n in enumerate(step_lens):
@@ -158,7 +159,7 @@ def test_state_space_mixer_between_its_products(heads, P, N, groups, taps, ngrou
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_clamped_swish_token_gate_fold_norm_and_scale(dtype):
+def test_clamped_swish_token_gate_fold_norm_and_scaled_products(dtype):
     from trapetum_b200.csrc import ops
     dt = DTYPES[dtype]
     g = torch.Generator().manual_seed(5)
@@ -188,8 +189,20 @@ def test_clamped_swish_token_gate_fold_norm_and_scale(dtype):
             assert rel(hd, want) <= 3e-6
             if out is not None:
                 assert torch.equal(out.cpu(), hd.to(dt).cpu())
-    x = torch.randn(4, 33, generator=g)
-    assert torch.equal(ops.scale_(x.clone().to(DEV), 0.3).cpu(), x * torch.tensor(0.3))
+    # a product whose epilogue scales: the 32-bit kernel and, in bfloat16, the tensor-core kernel (few and many tokens)
+    for rows in (5, 300):
+        x, wm = rnd(torch.randn(rows, 64, generator=g)), rnd(torch.randn(96, 64, generator=g))
+        want = (x.double() @ wm.double().T) * 0.3
+        got = ops.gemm_simt(x.to(DEV).to(dt), wm.to(DEV).to(dt), torch.float32, out_scale=0.3)
+        assert rel(got, want) <= 3e-6
+        if dtype == "bfloat16":
+            assert rel(ops.gemm_tc(x.to(DEV).to(dt), wm.to(DEV).to(dt), torch.float32, out_scale=0.3), want) <= 3e-6
+            # and the gate in the tensor-core product's epilogue
+            gw, uw = rnd(torch.randn(64, 64, generator=g)), rnd(torch.randn(64, 64, generator=g))
+            gg, uu = torch.clamp(x.double() @ gw.double().T, max=L), torch.clamp(x.double() @ uw.double().T, -L, L)
+            fused = ops.gemm_tc(x.to(DEV).to(dt), ops.interleave_gate_up(gw.to(DEV).to(dt), uw.to(DEV).to(dt)), dt,
+                                gated_act="clamped_swish", act_limit=L)
+            assert rel(fused, gg * torch.sigmoid(1.702 * gg) * (uu + 1)) <= 2 ** -7
 
 
 # =================================================================================================================
@@ -295,7 +308,7 @@ def test_unequal_batch_equals_each_alone_and_slots_are_reused(folders, oracles, 
             live = [i for i in live if i not in done]
         for i, s in enumerate(seqs):
             idx = [p for places, _ in got[i] for p in places]
-            close(torch.cat([o for _, o in got[i]]), truth[i][idx], tolerance(name, cfg, w, s, dtype),
+            close(torch.cat([o for _, o in got[i]]), truth[i][idx], tolerance(name, cfg, w, s, dtype)[idx],
                   f"{name} round {rep} sequence {i} of an unequal batch", dtype)
     eng.cache.check()
     eng.check_kernels()
@@ -345,14 +358,15 @@ def test_far_keys_and_page_borders(tmp_path, dim, heads, kv, dtype):
         tail = [eng.step(s1, [[ids[t]]], [[0]]).clone() for t in range(270, n)]
         eng.release(s1)
         tol = tolerance(("needle", dim), cfg, w, ids, dtype)
-        close(got, truth[250:251], tol, f"needle at {far}, asked in the prompt (head size {dim})", dtype)
-        close(tail[10], truth[280:281], tol, f"needle at {far}, asked in decoding (head size {dim})", dtype)
+        close(got, truth[250:251], tol[250:251], f"needle at {far}, asked in the prompt (head size {dim})", dtype)
+        close(tail[10], truth[280:281], tol[280:281], f"needle at {far}, asked in decoding (head size {dim})", dtype)
     eng.check_kernels()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_a_state_far_back_is_still_felt(tmp_path, dtype):
-    """A state-space layer that forgets slowly (small decay rate): the logits at the end depend on the first token."""
+    """A state-space layer that forgets slowly (small decay rate): what it gathered over a long prompt decides the
+    logits long after, so a state that is lost or reset on the way shows."""
     cfg = config(50, 32, [("mamba2", ssm(2, 16, 16, 1, 4, 1), None)], alpha=0.5)
     wts = random_weights(cfg, 1)
     wts["l0.mix.A_log"] = torch.full((2,), -6.0).to(torch.bfloat16)
@@ -360,14 +374,14 @@ def test_a_state_far_back_is_still_felt(tmp_path, dtype):
     folder = write_folder(str(tmp_path), cfg, wts)
     cfg, w = plain.load_folder(folder)
     (ids,) = prompts(50, [200], seed=1)
-    other = [(ids[0] + 7) % 50] + ids[1:]
-    ta, tb_ = plain.forward(cfg, w, ids), plain.forward(cfg, w, other)
-    assert logit_error(ta[-1:], tb_[-1:]) > 0.05                        # the first token matters at the end
+    ta = plain.forward(cfg, w, ids)
+    lost = plain.forward(cfg, w, ids[120:])                            # what a sequence that lost its state at 120 would say
+    assert logit_error(lost[-1:], ta[-1:]) > 0.2
     eng = tb.Engine(tb.load_model(folder, dtype, DEV), 64 * 4, max_slots=2)
     s = eng.start(1)
     got = [eng.step(s, [ids[:120]], [[119]])] + [eng.step(s, [[t]], [[0]]).clone() for t in ids[120:]]
     eng.release(s)
-    close(torch.cat(got), ta[119:], tolerance("slow", cfg, w, ids, dtype), "slow state, prompt then decoding", dtype)
+    close(torch.cat(got), ta[119:], tolerance("slow", cfg, w, ids, dtype)[119:], "slow state, prompt then decoding", dtype)
 
 
 @pytest.mark.parametrize("name", sorted(CONFIGS))
@@ -436,7 +450,7 @@ def test_trace_replay(folders, oracles, tmp_path, dtype):
     assert proc.returncode == 0, proc.stderr[-3000:]
     assert [l for l in proc.stdout.split("\n") if l.startswith("done")] == [f"done {s['step']}" for s in steps]
     assert sorted(os.listdir(out)) == sorted(f"{n}.f32" for n in expect)
-    tol = max(tolerance(name, cfg, w, r, dtype) for r in reqs)
+    tol = max(float(tolerance(name, cfg, w, r, dtype).max()) for r in reqs)
     for n, want in expect.items():
         got = torch.from_numpy(np.fromfile(os.path.join(out, f"{n}.f32"), dtype="<f4").reshape(-1, V))
         assert got.shape == want.shape

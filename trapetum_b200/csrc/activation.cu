@@ -8,8 +8,7 @@
 // clamped_swish is the gate of feed-forwards that bound both branches by a limit L:
 //   g' = min(g, L), u' = clamp(u, -L, L), out = g' sigmoid(1.702 g') (u' + 1).
 //
-// Also here: the per-token gate of a token-indexed side input (tb_token_gate), a plain scale
-// (tb_scale) and the bias row (tb_add_bias).
+// Also here: the per-token gate of a token-indexed side input (tb_token_gate) and the bias row (tb_add_bias).
 #include "common.cuh"
 
 TB_EXPORT_ERROR()
@@ -90,32 +89,22 @@ __global__ void token_gate_kernel(const TI* __restrict__ g, const int* __restric
 }
 
 extern "C" int tb_token_gate(const void* g, int g_dtype, const int* ids, const void* table, int table_dtype,
-                             long long table_stride, int col0, int vocab, void* out, int rows, int dim, cudaStream_t stream) {
+                             long long table_stride, int col0, int vocab, void* out, int out_dtype, int rows, int dim,
+                             cudaStream_t stream) {
     if (rows <= 0 || dim <= 0) return 0;
     dim3 grid(rows, (dim + 127) / 128);
     if (grid.y > 65535) return tb_refuse("token_gate: dim %d is too wide", dim);
-#define LAUNCH(TI, TW) tb_launch(token_gate_kernel<TI, TW, TI>, dim3(grid), dim3(128), 0, stream, (const TI*)g, ids, \
-                                 (const TW*)table, table_stride, col0, vocab, (TI*)out, dim)
-    if (g_dtype == TB_F32 && table_dtype == TB_F32) LAUNCH(float, float);
-    else if (g_dtype == TB_F32 && table_dtype == TB_BF16) LAUNCH(float, bf16);
-    else if (g_dtype == TB_BF16 && table_dtype == TB_BF16) LAUNCH(bf16, bf16);
-    else if (g_dtype == TB_BF16 && table_dtype == TB_F32) LAUNCH(bf16, float);
+#define LAUNCH(TI, TW, TO) tb_launch(token_gate_kernel<TI, TW, TO>, dim3(grid), dim3(128), 0, stream, (const TI*)g, ids, \
+                                     (const TW*)table, table_stride, col0, vocab, (TO*)out, dim)
+#define LAUNCH_O(TI, TW) do { if (out_dtype == TB_F32) LAUNCH(TI, TW, float); else LAUNCH(TI, TW, bf16); } while (0)
+    if (out_dtype != TB_F32 && out_dtype != TB_BF16) return tb_refuse("token_gate: unknown output dtype %d", out_dtype);
+    if (g_dtype == TB_F32 && table_dtype == TB_F32) LAUNCH_O(float, float);
+    else if (g_dtype == TB_F32 && table_dtype == TB_BF16) LAUNCH_O(float, bf16);
+    else if (g_dtype == TB_BF16 && table_dtype == TB_BF16) LAUNCH_O(bf16, bf16);
+    else if (g_dtype == TB_BF16 && table_dtype == TB_F32) LAUNCH_O(bf16, float);
     else return tb_refuse("token_gate: unknown dtype codes %d %d", g_dtype, table_dtype);
+#undef LAUNCH_O
 #undef LAUNCH
-    return tb_launch_status();
-}
-
-// x *= s in place (32-bit).
-__global__ void scale_kernel(float* __restrict__ x, float s, size_t n) {
-    pdl_launch_dependents();
-    pdl_wait();
-    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) x[i] *= s;
-}
-
-extern "C" int tb_scale(float* x, float s, long long n, cudaStream_t stream) {
-    if (n <= 0) return 0;
-    tb_launch(scale_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, s, (size_t)n);
     return tb_launch_status();
 }
 

@@ -21,7 +21,7 @@ TB_EXPORT_ERROR()
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C,
-                 int M, int N, int K, long long lda, long long ldw, long long ldc, float cap) {
+                 int M, int N, int K, long long lda, long long ldw, long long ldc, float cap, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float As[BK][BM + 4];
@@ -80,21 +80,22 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restr
             if (n >= N) continue;
             float v = acc[i][j];
             if (cap > 0.f) v = softcap_f(v, cap);
-            C[(size_t)m * ldc + n] = from_f<TC>(v);
+            C[(size_t)m * ldc + n] = from_f<TC>(v * scale);
         }
     }
 }
 
-extern "C" int tb_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype,
-                            int M, int N, int K, long long lda, long long ldw, long long ldc,
-                            float softcap, cudaStream_t stream) {
+// out_scale: the output times this number (1: a plain product), applied after the cap.
+extern "C" int tb_gemm_simt_ex(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype,
+                               int M, int N, int K, long long lda, long long ldw, long long ldc,
+                               float softcap, float out_scale, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return tb_refuse("gemm: K=%d", K);
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return tb_refuse("gemm: M=%d is too many rows for one call", M);
     const int key = (a_dtype << 2) | (w_dtype << 1) | c_dtype;
 #define LAUNCH(TA, TW, TC) tb_launch(gemm_simt_kernel<TA, TW, TC>, dim3(grid), dim3(256), 0, stream,  \
-        (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc, softcap)
+        (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc, softcap, out_scale)
     switch (key) {
     case 0: LAUNCH(float, float, float); break;
     case 1: LAUNCH(float, float, bf16); break;
@@ -108,4 +109,10 @@ extern "C" int tb_gemm_simt(const void* A, int a_dtype, const void* W, int w_dty
     }
 #undef LAUNCH
     return tb_launch_status();
+}
+
+extern "C" int tb_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype,
+                            int M, int N, int K, long long lda, long long ldw, long long ldc,
+                            float softcap, cudaStream_t stream) {
+    return tb_gemm_simt_ex(A, a_dtype, W, w_dtype, C, c_dtype, M, N, K, lda, ldw, ldc, softcap, 1.0f, stream);
 }

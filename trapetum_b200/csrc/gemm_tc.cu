@@ -51,7 +51,9 @@ struct GemmParams {
     void* out; long long ld_out;     // C as [tokens, weight rows], row stride ld_out
     float* partial;                  // [splits][tokens][weight rows] when splits > 1
     float cap;
-    int act;                         // gated epilogue: 0 gelu_tanh, 1 silu (only with GATED kernels)
+    float scale;                     // the output times this (1 for a plain product); after the cap, never with it
+    int act;                         // gated epilogue: 0 gelu_tanh, 1 silu, 2 clamped_swish (only with GATED kernels)
+    float limit;                     // clamped_swish: both branches are bounded by it
 };
 
 // Gated epilogue.  The weight rows are interleaved in blocks of 16: [gate 0..15 | up 0..15 | gate 16..31 | ...],
@@ -61,8 +63,13 @@ struct GemmParams {
 // (the reference's gelu_mul_k does this as a kernel of its own, runtime/cuda/codebook_gemv.cu:531-537).
 // The result is rounded to bfloat16, so tanh and the logistic function are taken through the fast exponential
 // and division (relative error near 2^-21): 0.5 (1 + tanh(y)) = 1 / (1 + e^(-2y)).
-__device__ __forceinline__ float gated(float g, float u, int act) {
-    const float y = act == 0 ? 1.5957691216f * (g + 0.044715f * g * g * g) : g;     // 2 sqrt(2/pi) (g + 0.044715 g^3)
+// clamped_swish: g' = min(g, L), u' = clamp(u, -L, L), g' / (1 + e^(-1.702 g')) * (u' + 1).
+__device__ __forceinline__ float gated(float g, float u, int act, float limit) {
+    if (act == 2) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+    }
+    const float y = act == 0 ? 1.5957691216f * (g + 0.044715f * g * g * g) : (act == 2 ? 1.702f * g : g);     // 2 sqrt(2/pi) (g + 0.044715 g^3)
     return __fdividef(g, 1.0f + __expf(-y)) * u;
 }
 
@@ -104,8 +111,8 @@ __device__ __forceinline__ void store_token_major(const uint32_t* r, int prow, i
             uint32_t w[8];
 #pragma unroll
             for (int j = 0; j < 16; j += 2) {
-                const float v0 = gated(__uint_as_float(r[j]), __uint_as_float(r[j + 16]), p.act);
-                const float v1 = gated(__uint_as_float(r[j + 1]), __uint_as_float(r[j + 17]), p.act);
+                const float v0 = gated(__uint_as_float(r[j]), __uint_as_float(r[j + 16]), p.act, p.limit);
+                const float v1 = gated(__uint_as_float(r[j + 1]), __uint_as_float(r[j + 17]), p.act, p.limit);
                 __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
                 w[j >> 1] = *(uint32_t*)&h2;
             }
@@ -135,6 +142,7 @@ __device__ __forceinline__ void store_token_major(const uint32_t* r, int prow, i
                         for (int e = 0; e < 4; e++) {
                             float v0 = __uint_as_float(r[j + 2 * e]), v1 = __uint_as_float(r[j + 2 * e + 1]);
                             if (p.cap > 0.f) { v0 = softcap_f(v0, p.cap); v1 = softcap_f(v1, p.cap); }
+                            v0 *= p.scale; v1 *= p.scale;
                             __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
                             w[e] = *(uint32_t*)&h2;
                         }
@@ -147,6 +155,7 @@ __device__ __forceinline__ void store_token_major(const uint32_t* r, int prow, i
                                                __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
                         if (p.cap > 0.f) { v.x = softcap_f(v.x, p.cap); v.y = softcap_f(v.y, p.cap);
                                            v.z = softcap_f(v.z, p.cap); v.w = softcap_f(v.w, p.cap); }
+                        v.x *= p.scale; v.y *= p.scale; v.z *= p.scale; v.w *= p.scale;
                         *(float4*)((float*)dst + j) = v;
                     }
                 } else {
@@ -154,7 +163,7 @@ __device__ __forceinline__ void store_token_major(const uint32_t* r, int prow, i
                     for (int j = 0; j < CH; j++) if (q0 + j < p.rows_q) {
                         float v = __uint_as_float(r[j]);
                         if (p.cap > 0.f) v = softcap_f(v, p.cap);
-                        dst[j] = from_f<TOut>(v);
+                        dst[j] = from_f<TOut>(v * p.scale);
                     }
                 }
             }
@@ -315,7 +324,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                         const float u = low ? got : __uint_as_float(r[j + 1]);
                         const int tok = q0 + j + (low ? 0 : 1);
                         if (tok < p.rows_q && prow < p.rows_p)
-                            ((bf16*)p.out)[(size_t)tok * p.ld_out + feat] = __float2bfloat16_rn(gated(g, u, p.act));
+                            ((bf16*)p.out)[(size_t)tok * p.ld_out + feat] = __float2bfloat16_rn(gated(g, u, p.act, p.limit));
                     }
                 } else {
                     // weight rows on lanes (prow), tokens on columns (q0 + j): lanes write neighbours
@@ -329,7 +338,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                                 p.partial[((size_t)sp * p.rows_q + tok) * p.rows_p + prow] = v;
                             } else {
                                 if (p.cap > 0.f) v = softcap_f(v, p.cap);
-                                ((TOut*)p.out)[(size_t)tok * p.ld_out + prow] = from_f<TOut>(v);
+                                ((TOut*)p.out)[(size_t)tok * p.ld_out + prow] = from_f<TOut>(v * p.scale);
                             }
                         }
                     }
@@ -520,7 +529,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 // partial[splits][rows][cols] summed in split order, then cap and conversion.
 template <typename TOut>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TOut* __restrict__ out, int rows, int cols,
-                                     long long ld_out, int splits, float cap) {
+                                     long long ld_out, int splits, float cap, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -529,7 +538,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TOut* __
     float s = 0.f;
     for (int k = 0; k < splits; k++) s += partial[(size_t)k * n + i];
     if (cap > 0.f) s = softcap_f(s, cap);
-    out[(i / cols) * ld_out + (i % cols)] = from_f<TOut>(s);
+    out[(i / cols) * ld_out + (i % cols)] = from_f<TOut>(s * scale);
 }
 
 // ---------------------------------------------------------------------------
@@ -667,9 +676,11 @@ extern "C" int tb_gemm_tc_effective_splits(int K, int splits) {
 }
 
 // reduce = 0 with splits > 1: leave the partial sums in `scratch` ([splits][M][N]) for the consumer to add.
-extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,
-                          long long lda, long long ldw, long long ldc, float softcap, int splits, float* scratch,
-                          int reduce, int gated_act, cudaStream_t stream) {
+// out_scale: the output times this number (1: a plain product; not with a cap, not on partial sums that are left).
+// act_limit: the limit of the gated activation 2 (clamped_swish).
+extern "C" int tb_gemm_tc_ex(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,
+                             long long lda, long long ldw, long long ldc, float softcap, int splits, float* scratch,
+                             int reduce, int gated_act, float act_limit, float out_scale, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!tb_gemm_tc_takes(A, W, M, N, K, lda, ldw))
         return tb_refuse("gemm_tc: needs K, lda, ldw multiples of 8 and 16-byte aligned operands "
@@ -688,7 +699,8 @@ extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
     if (splits > 1 && scratch == nullptr) return tb_refuse("gemm_tc: split-K needs scratch");
     const bool gated = gated_act >= 0;
     if (gated) {
-        if (gated_act > 1) return tb_refuse("gemm_tc: unknown gated activation %d", gated_act);
+        if (gated_act > 2) return tb_refuse("gemm_tc: unknown gated activation %d", gated_act);
+        if (gated_act == 2 && !(act_limit > 0.f)) return tb_refuse("gemm_tc: clamped_swish needs a positive limit");
         if (N % 32) return tb_refuse("gemm_tc: the gated epilogue needs a multiple of 32 weight rows, got %d", N);
         if (c_dtype != TB_BF16) return tb_refuse("gemm_tc: the gated epilogue writes bfloat16");
         if (softcap > 0.f) return tb_refuse("gemm_tc: the gated epilogue takes no soft cap");
@@ -706,6 +718,10 @@ extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
     p.K = K; p.kblocks = kblocks; p.splits = splits; p.kb_per_split = per;
     p.out = C; p.ld_out = ldc; p.partial = scratch; p.cap = splits > 1 ? 0.f : softcap;
     p.act = gated ? gated_act : 0;
+    p.limit = act_limit;
+    if (out_scale != 1.0f && (softcap > 0.f || gated || (splits > 1 && !reduce)))
+        return tb_refuse("gemm_tc: an output scale goes with neither a cap, a gated epilogue nor partial sums");
+    p.scale = splits > 1 ? 1.0f : out_scale;
     CUtensorMap mp, mq;
     if (swap) {
         p.rows_p = N; p.rows_q = M;
@@ -749,12 +765,19 @@ extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, in
         const size_t n = (size_t)M * N;
         const unsigned blocks = (unsigned)((n + 255) / 256);
         if (c_dtype == TB_BF16)
-            tb_launch(splitk_reduce_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, scratch, (bf16*)C, M, N, ldc, splits, softcap);
+            tb_launch(splitk_reduce_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, scratch, (bf16*)C, M, N, ldc, splits, softcap, out_scale);
         else
-            tb_launch(splitk_reduce_kernel<float>, dim3(blocks), dim3(256), 0, stream, scratch, (float*)C, M, N, ldc, splits, softcap);
+            tb_launch(splitk_reduce_kernel<float>, dim3(blocks), dim3(256), 0, stream, scratch, (float*)C, M, N, ldc, splits, softcap, out_scale);
         st = tb_launch_status();
     }
     return st;
+}
+
+extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,
+                          long long lda, long long ldw, long long ldc, float softcap, int splits, float* scratch,
+                          int reduce, int gated_act, cudaStream_t stream) {
+    if (gated_act > 1) return tb_refuse("gemm_tc: gated activation %d needs its parameter (tb_gemm_tc_ex)", gated_act);
+    return tb_gemm_tc_ex(A, W, C, c_dtype, M, N, K, lda, ldw, ldc, softcap, splits, scratch, reduce, gated_act, 0.f, 1.0f, stream);
 }
 
 // out[rows][cols] = sum over splits, in order, of partial[s][rows][cols] (32-bit).
@@ -763,7 +786,7 @@ extern "C" int tb_sum_partials(const float* partial, float* out, int rows, int c
     if (n == 0) return 0;
     if (splits < 1) return tb_refuse("sum_partials: splits=%d", splits);
     tb_launch(splitk_reduce_kernel<float>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream,
-              partial, out, rows, cols, (long long)cols, splits, 0.f);
+              partial, out, rows, cols, (long long)cols, splits, 0.f, 1.0f);
     return tb_launch_status();
 }
 

@@ -13,7 +13,8 @@
 // (row = ring_rows ? pos % ring_rows : pos, page = page_table[seq, row / page_rows]; in a ring only tokens
 // with pos >= len_after - ring_rows are written, as the rotary kernel does).
 //
-// One warp per (token, head slot); a lane holds elements lane, lane + 32, ... of the head.
+// One warp per (token, head slot); a lane holds groups of four neighbouring elements of the head (single elements
+// when a size or an address does not allow 16-byte accesses).
 #include "common.cuh"
 
 TB_EXPORT_ERROR()
@@ -30,10 +31,20 @@ struct HeadNormKvArgs {
 
 #define HN_MAX_PER_LANE 16        // head_dim <= 512
 
-template <typename T>
+template <typename T> __device__ __forceinline__ void store4(T* p, const float* f);
+template <> __device__ __forceinline__ void store4<float>(float* p, const float* f) { *(float4*)p = make_float4(f[0], f[1], f[2], f[3]); }
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, const float* f) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    *(uint2*)p = make_uint2(*(uint32_t*)&a, *(uint32_t*)&b);
+}
+
+// VEC = 4: head_dim and all row strides are multiples of 4 and the bases 16-byte aligned; a lane then holds groups of
+// four neighbouring elements (one 16-byte load per split, one 8- or 16-byte store per destination).
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256) headnorm_kv_kernel(HeadNormKvArgs a, int n_tokens) {
     pdl_launch_dependents();
     pdl_wait();
+    constexpr int GROUPS = HN_MAX_PER_LANE / VEC;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int in_slots = a.n_heads + a.n_kv_heads * (a.v_from_k ? 1 : 2);
     const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
@@ -46,17 +57,25 @@ __global__ void __launch_bounds__(256) headnorm_kv_kernel(HeadNormKvArgs a, int 
     const float* src = a.partial + (size_t)t * a.partial_row_stride + (size_t)hs * hd;
     const int pos = a.positions[t];
 
-    float x[HN_MAX_PER_LANE];
+    float x[GROUPS][VEC];
     float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < HN_MAX_PER_LANE; k++) {
-        const int i = lane + 32 * k;
-        x[k] = 0.f;
+    for (int k = 0; k < GROUPS; k++) {
+        const int i = (lane + 32 * k) * VEC;
+#pragma unroll
+        for (int e = 0; e < VEC; e++) x[k][e] = 0.f;
         if (i < hd) {
-            float v = src[i];
-            for (int s = 1; s < a.n_splits; s++) v += src[(size_t)s * a.split_stride + i];
-            x[k] = v;
-            ss += v * v;
+            for (int s = 0; s < a.n_splits; s++) {                   // added in split order
+                const float* q = src + (size_t)s * a.split_stride + i;
+                if (VEC == 4) {
+                    const float4 v = *(const float4*)q;
+                    x[k][0] += v.x; x[k][1] += v.y; x[k][2] += v.z; x[k][3] += v.w;
+                } else {
+                    x[k][0] += q[0];
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < VEC; e++) ss += x[k][e] * x[k][e];
         }
     }
     float f = 1.f;
@@ -88,16 +107,21 @@ __global__ void __launch_bounds__(256) headnorm_kv_kernel(HeadNormKvArgs a, int 
     T* o_v = also_v ? row + v_off + kvh * hd : nullptr;
     T* c_v = (also_v && store) ? (T*)a.v_pool + cache_off : nullptr;
 #pragma unroll
-    for (int k = 0; k < HN_MAX_PER_LANE; k++) {
-        const int i = lane + 32 * k;
+    for (int k = 0; k < GROUPS; k++) {
+        const int i = (lane + 32 * k) * VEC;
         if (i < hd) {
-            const T y = from_f<T>(x[k] * f);
-            o_main[i] = y;
-            if (c_main) c_main[i] = y;
-            if (also_v) {
-                const T raw = from_f<T>(x[k]);
-                o_v[i] = raw;
-                if (c_v) c_v[i] = raw;
+            float y[VEC];
+#pragma unroll
+            for (int e = 0; e < VEC; e++) y[e] = x[k][e] * f;
+            if (VEC == 4) {
+                store4<T>(o_main + i, y);
+                if (c_main) store4<T>(c_main + i, y);
+                if (also_v) { store4<T>(o_v + i, x[k]); if (c_v) store4<T>(c_v + i, x[k]); }
+            } else {
+                const T yy = from_f<T>(y[0]);
+                o_main[i] = yy;
+                if (c_main) c_main[i] = yy;
+                if (also_v) { const T raw = from_f<T>(x[k][0]); o_v[i] = raw; if (c_v) c_v[i] = raw; }
             }
         }
     }
@@ -118,6 +142,10 @@ extern "C" int tb_headnorm_kv(const HeadNormKvArgs* args, int out_dtype, int n_t
     const long long items = (long long)n_tokens * in_slots;
     const long long blocks = (items + 7) / 8;
     if (blocks > 0x7fffffffLL) return tb_refuse("headnorm_kv: too many tokens");
-    TB_DISPATCH_1(out_dtype, T, tb_launch(headnorm_kv_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, a, n_tokens));
+    auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    const bool vec = a.head_dim % 4 == 0 && a.split_stride % 4 == 0 && a.partial_row_stride % 4 == 0 &&
+                     a.out_row_stride % 4 == 0 && al16(a.partial) && al16(a.out) && al16(a.k_pool) && al16(a.v_pool);
+    if (vec) TB_DISPATCH_1(out_dtype, T, tb_launch(headnorm_kv_kernel<T, 4>, dim3((unsigned)blocks), dim3(256), 0, stream, a, n_tokens));
+    else TB_DISPATCH_1(out_dtype, T, tb_launch(headnorm_kv_kernel<T, 1>, dim3((unsigned)blocks), dim3(256), 0, stream, a, n_tokens));
     return tb_launch_status();
 }

@@ -1,7 +1,8 @@
 // A selective state-space mixer (the Mamba-2 recurrence) between its input and output products.
 //
-// The input product gives a row [z: inner | xBC: channels | dt: heads] per token, inner = heads * P,
-// channels = inner + 2 * groups * N.  Three kernels:
+// The input product gives a row [z: inner | xBC: channels] per token in the compute dtype and the step sizes
+// [dt: heads] in 32-bit (they enter an exponential), inner = heads * P, channels = inner + 2 * groups * N.
+// Three kernels:
 //
 //   tb_mamba2_conv       u = silu(bias + sum_j w[c][j] * in[t - (taps-1) + j][c]) over the token's own sequence,
 //                        rows before the step's first token come from the sequence's state (zeros at its start);
@@ -23,7 +24,8 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v));
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
 struct Mamba2Args {
-    const void* proj; long long proj_stride;      // [tokens][inner + channels + heads], compute dtype
+    const void* proj; long long proj_stride;      // [tokens][inner + channels], compute dtype
+    const float* dt; long long dt_stride;          // [tokens][heads], the step sizes before bias and softplus
     int heads, P, N, groups, taps, norm_groups;
     const void* conv_w; const void* conv_b;        // [channels][taps], [channels]   (weights' dtype)
     const void* dt_bias; const void* A_log; const void* D;   // [heads]
@@ -105,79 +107,189 @@ __global__ void mamba2_conv_step_kernel(Mamba2Args a) {
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// The recurrence.  A CTA of 128 threads owns (sequence, head, 16 values of P): thread (pl, ns) holds the NPT states
-// S[p][ns * NPT .. (ns + 1) * NPT) in registers (eight threads share a p and add their parts of y by shuffles).  B and
-// C of TT tokens at a time are staged in shared memory.
+// The recurrence.  A CTA owns (sequence, head, PT values of P): thread (pl, ns) keeps the states S[p][n] of two
+// neighbouring p with n = (k * 8 + ns) * 4 + e (k < NV, e < 4) in registers, so that the eight threads of a pair read
+// B and C of a token as eight neighbouring 16-byte words of shared memory (no bank conflict) and use each word for
+// both p.  B, C,
+// x, dt and the decay of TT tokens at a time are staged in shared memory; the next tile's values are requested into
+// registers before this tile's steps run, so that the loads' latency hides behind the recurrence.  A thread's parts of
+// the 2 TT outputs stay in registers and are added over the eight threads once per tile, off the dependency chain, by
+// a butterfly in which every thread hands over half of what it holds at each of the three stages.
 #define SCAN_NS 8
-#define SCAN_PT 16
 #define SCAN_TT 16
+#define SCAN_PP 2
 
-template <typename T, typename TW, int NPT>
-__global__ void __launch_bounds__(SCAN_NS * SCAN_PT) mamba2_scan_kernel(Mamba2Args a) {
+template <typename T> struct Chunk8;                                 // eight neighbouring values of the compute dtype
+template <> struct Chunk8<bf16> {
+    uint4 v;
+    __device__ __forceinline__ void load(const bf16* p) { v = *(const uint4*)p; }
+    __device__ __forceinline__ void zero() { v = make_uint4(0, 0, 0, 0); }
+    __device__ __forceinline__ void store(float* d) const {
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) { f[2 * i] = __uint_as_float(u[i] << 16); f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
+        *(float4*)d = make_float4(f[0], f[1], f[2], f[3]);
+        *(float4*)(d + 4) = make_float4(f[4], f[5], f[6], f[7]);
+    }
+};
+template <> struct Chunk8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) { a = *(const float4*)p; b = *(const float4*)(p + 4); }
+    __device__ __forceinline__ void zero() { a = b = make_float4(0.f, 0.f, 0.f, 0.f); }
+    __device__ __forceinline__ void store(float* d) const { *(float4*)d = a; *(float4*)(d + 4) = b; }
+};
+
+// VEC8: N is a multiple of 8 and the rows of B and C start on 16-byte boundaries.
+template <typename T, typename TW, int NV, int PT, bool VEC8>
+__global__ void __launch_bounds__(SCAN_NS * PT / SCAN_PP) mamba2_scan_kernel(Mamba2Args a) {
     pdl_launch_dependents();
-    extern __shared__ float sh[];                                    // [TT][2][N] B and C, then [TT][PT] x, then [TT][2] dt and decay
+    constexpr int NP = NV * 32;                                      // padded state size (zeros beyond N)
+    constexpr int THREADS = SCAN_NS * PT / SCAN_PP;
+    constexpr int CHUNKS = SCAN_TT * 2 * NP / 8;                     // 8-value chunks of B and C in a tile
+    constexpr int CPT = (CHUNKS + THREADS - 1) / THREADS;            // chunks a thread fetches
+    constexpr int XPT = SCAN_TT * PT / THREADS;                      // x values a thread fetches (4)
+    extern __shared__ __align__(16) float sh[];                      // [TT][NP] B, [TT][NP] C, [TT][PT] x, [TT][2] dt and decay
     const int N = a.N, P = a.P, H = a.heads;
     const int inner = H * P, ch = inner + 2 * a.groups * N;
-    const int b = blockIdx.z, h = blockIdx.y, p0 = blockIdx.x * SCAN_PT;
+    const int b = blockIdx.z, h = blockIdx.y, p0 = blockIdx.x * PT;
     const int g = h / (H / a.groups);
     const int ns = threadIdx.x % SCAN_NS, pl = threadIdx.x / SCAN_NS;
-    const int p = p0 + pl;
-    const int n0 = ns * NPT;
-    float* sBC = sh;
-    float* sx = sh + SCAN_TT * 2 * N;
-    float* sdt = sx + SCAN_TT * SCAN_PT;
+    const int p = p0 + pl * SCAN_PP;                                 // this thread's first p
+    float* sB = sh;
+    float* sC = sh + SCAN_TT * NP;
+    float* sx = sC + SCAN_TT * NP;
+    float* sdt = sx + SCAN_TT * PT;
     const float A = -expf(to_f<TW>(((const TW*)a.A_log)[h]));
     const float Dh = to_f<TW>(((const TW*)a.D)[h]);
     const float dtb = to_f<TW>(((const TW*)a.dt_bias)[h]);
     pdl_wait();
     const int s0 = a.seq_start[b], s1 = a.seq_start[b + 1];
-    float* S = a.state + (size_t)a.slot_ids[b] * a.state_stride + ((size_t)h * P + (p < P ? p : 0)) * N;
-    float s[NPT];
+    float* S = a.state + (size_t)a.slot_ids[b] * a.state_stride + (size_t)h * P * N;
+    float s[SCAN_PP][NV][4];
 #pragma unroll
-    for (int k = 0; k < NPT; k++) s[k] = (p < P && n0 + k < N) ? S[n0 + k] : 0.f;
+    for (int j = 0; j < SCAN_PP; j++)
+#pragma unroll
+        for (int k = 0; k < NV; k++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int n = (k * SCAN_NS + ns) * 4 + e;
+                s[j][k][e] = (p + j < P && n < N) ? S[(size_t)(p + j) * N + n] : 0.f;
+            }
     const T* xbc = (const T*)a.xbc;
-    const T* proj = (const T*)a.proj;
+
+    Chunk8<T> pre[VEC8 ? CPT : 1];
+    float pre_x[XPT], pre_dt = 0.f;
+    auto fetch = [&](int tb) {                                       // the tile that starts at token tb, into registers
+        const int nt = min(SCAN_TT, s1 - tb);
+        if (VEC8) {
+#pragma unroll
+            for (int l = 0; l < CPT; l++) {
+                const int c = threadIdx.x + l * THREADS;
+                const int tt = c / (2 * NP / 8), r = c % (2 * NP / 8);
+                const int n8 = (r % (NP / 8)) * 8;
+                pre[l].zero();
+                if (c < CHUNKS && tt < nt && n8 < N)
+                    pre[l].load(xbc + (size_t)(tb + tt) * ch + inner + g * N + (r >= NP / 8 ? a.groups * N : 0) + n8);
+            }
+        }
+#pragma unroll
+        for (int l = 0; l < XPT; l++) {
+            const int i = threadIdx.x + l * THREADS;
+            const int tt = i / PT, pp = p0 + i % PT;
+            pre_x[l] = (tt < nt && pp < P) ? to_f<T>(xbc[(size_t)(tb + tt) * ch + h * P + pp]) : 0.f;
+        }
+        if (threadIdx.x < nt) pre_dt = a.dt[(size_t)(tb + threadIdx.x) * a.dt_stride + h];
+    };
+    auto commit = [&](int tb) {                                      // registers (or, without VEC8, memory) to shared memory
+        const int nt = min(SCAN_TT, s1 - tb);
+        if (VEC8) {
+#pragma unroll
+            for (int l = 0; l < CPT; l++) {
+                const int c = threadIdx.x + l * THREADS;
+                const int tt = c / (2 * NP / 8), r = c % (2 * NP / 8);
+                if (c < CHUNKS) pre[l].store((r >= NP / 8 ? sC : sB) + tt * NP + (r % (NP / 8)) * 8);
+            }
+        } else {
+            for (int i = threadIdx.x; i < nt * NP; i += THREADS) {
+                const int tt = i / NP, n = i % NP;
+                const T* row = xbc + (size_t)(tb + tt) * ch + inner + g * N;
+                sB[i] = n < N ? to_f<T>(row[n]) : 0.f;
+                sC[i] = n < N ? to_f<T>(row[a.groups * N + n]) : 0.f;
+            }
+        }
+#pragma unroll
+        for (int l = 0; l < XPT; l++) sx[threadIdx.x + l * THREADS] = pre_x[l];
+        if (threadIdx.x < nt) {
+            const float dt = softplus_f(pre_dt + dtb);
+            sdt[2 * threadIdx.x] = dt;
+            sdt[2 * threadIdx.x + 1] = expf(A * dt);
+        }
+    };
+
+    if (s0 < s1) fetch(s0);
     for (int tb = s0; tb < s1; tb += SCAN_TT) {
         const int nt = min(SCAN_TT, s1 - tb);
+        __syncthreads();                                             // the last tile's steps have read shared memory
+        commit(tb);
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * 2 * N; i += blockDim.x) {
-            const int tt = i / (2 * N), r = i % (2 * N);             // r < N: B, else C
-            const int col = inner + (r < N ? g * N + r : a.groups * N + g * N + (r - N));
-            sBC[i] = to_f<T>(xbc[(size_t)(tb + tt) * ch + col]);
-        }
-        for (int i = threadIdx.x; i < nt * SCAN_PT; i += blockDim.x) {
-            const int tt = i / SCAN_PT, pp = p0 + i % SCAN_PT;
-            sx[i] = pp < P ? to_f<T>(xbc[(size_t)(tb + tt) * ch + h * P + pp]) : 0.f;
-        }
-        for (int i = threadIdx.x; i < nt; i += blockDim.x) {
-            const float dt = softplus_f(to_f<T>(proj[(size_t)(tb + i) * a.proj_stride + inner + ch + h]) + dtb);
-            sdt[2 * i] = dt;
-            sdt[2 * i + 1] = expf(A * dt);
-        }
-        __syncthreads();
-        for (int tt = 0; tt < nt; tt++) {
-            const float dt = sdt[2 * tt], dec = sdt[2 * tt + 1];
-            const float x = sx[tt * SCAN_PT + pl];
-            const float dx = dt * x;
-            const float* Bt = sBC + (size_t)tt * 2 * N;
-            const float* Ct = Bt + N;
-            float y = 0.f;
+        if (tb + SCAN_TT < s1) fetch(tb + SCAN_TT);
+        float yp[SCAN_TT * SCAN_PP];                                 // yp[tt * 2 + j]: this thread's part of y of token tt, p + j
 #pragma unroll
-            for (int k = 0; k < NPT; k++) {
-                if (n0 + k < N) {
-                    s[k] = dec * s[k] + dx * Bt[n0 + k];
-                    y += s[k] * Ct[n0 + k];
+        for (int tt = 0; tt < SCAN_TT; tt++) {
+            yp[2 * tt] = yp[2 * tt + 1] = 0.f;
+            if (tt < nt) {                                           // the same in every thread of the CTA
+                const float dec = sdt[2 * tt + 1], dt = sdt[2 * tt];
+                const float dx0 = dt * sx[tt * PT + pl * SCAN_PP], dx1 = dt * sx[tt * PT + pl * SCAN_PP + 1];
+                const float4* Bt = (const float4*)(sB + tt * NP);
+                const float4* Ct = (const float4*)(sC + tt * NP);
+                float y0[4] = {0.f, 0.f, 0.f, 0.f}, y1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int k = 0; k < NV; k++) {
+                    const float4 bv = Bt[k * SCAN_NS + ns], cv = Ct[k * SCAN_NS + ns];
+                    const float bb[4] = {bv.x, bv.y, bv.z, bv.w}, cc[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        s[0][k][e] = dec * s[0][k][e] + dx0 * bb[e]; y0[e] += s[0][k][e] * cc[e];
+                        s[1][k][e] = dec * s[1][k][e] + dx1 * bb[e]; y1[e] += s[1][k][e] * cc[e];
+                    }
+                }
+                yp[2 * tt] = (y0[0] + y0[1]) + (y0[2] + y0[3]);
+                yp[2 * tt + 1] = (y1[0] + y1[1]) + (y1[2] + y1[3]);
+            }
+        }
+        // the eight threads of a pair add their parts: at each stage a thread keeps one half of its values and hands
+        // the other to its partner; thread ns ends with the sums of tokens 2 ns and 2 ns + 1, both p
+#pragma unroll
+        for (int o = SCAN_NS / 2, half = SCAN_TT * SCAN_PP / 2; o > 0; o >>= 1, half >>= 1) {
+            const bool up = (ns & o) != 0;
+#pragma unroll
+            for (int i = 0; i < SCAN_TT * SCAN_PP / 2; i++) {
+                if (i < half) {
+                    const float keep = up ? yp[i + half] : yp[i];
+                    const float send = up ? yp[i] : yp[i + half];
+                    yp[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
                 }
             }
+        }
 #pragma unroll
-            for (int o = SCAN_NS / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-            if (ns == 0 && p < P) a.y[(size_t)(tb + tt) * inner + h * P + p] = y + Dh * x;
+        for (int r = 0; r < 4; r++) {
+            const int tt = 2 * ns + (r >> 1), j = r & 1;
+            if (tt < nt && p + j < P)
+                a.y[(size_t)(tb + tt) * inner + h * P + p + j] = yp[r] + Dh * sx[tt * PT + pl * SCAN_PP + j];
         }
     }
-    if (p < P) {
 #pragma unroll
-        for (int k = 0; k < NPT; k++) if (n0 + k < N) S[n0 + k] = s[k];
-    }
+    for (int j = 0; j < SCAN_PP; j++)
+        if (p + j < P) {
+#pragma unroll
+            for (int k = 0; k < NV; k++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int n = (k * SCAN_NS + ns) * 4 + e;
+                    if (n < N) S[(size_t)(p + j) * N + n] = s[j][k][e];
+                }
+        }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -250,13 +362,30 @@ extern "C" int tb_mamba2_scan(const Mamba2Args* args, int dtype, int w_dtype, cu
     Mamba2Args a = *args;
     if (a.n_tokens <= 0) return 0;
     if (check(a)) return -1;
-    const dim3 grid((a.P + SCAN_PT - 1) / SCAN_PT, a.heads, a.batch);
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0; cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    // thirty-two values of P a CTA (128 threads), or sixteen where that would leave SMs without work
+    const int pt = ((long long)((a.P + 31) / 32) * a.heads * a.batch >= 2LL * sms) ? 32 : 16;
+    const dim3 grid((a.P + pt - 1) / pt, a.heads, a.batch);
     if (grid.y > 65535 || grid.z > 65535) return tb_refuse("mamba2: too many heads or sequences for one launch");
-    const size_t smem = (size_t)(SCAN_TT * 2 * a.N + SCAN_TT * SCAN_PT + SCAN_TT * 2) * sizeof(float);
-    const int npt = (a.N + SCAN_NS - 1) / SCAN_NS;
-#define SCAN(NPT_) DISPATCH2(dtype, w_dtype, tb_launch(mamba2_scan_kernel<T, TW, NPT_>, dim3(grid), dim3(SCAN_NS * SCAN_PT), smem, stream, a))
-    if (npt <= 2) SCAN(2); else if (npt <= 4) SCAN(4); else if (npt <= 8) SCAN(8); else if (npt <= 16) SCAN(16); else SCAN(32);
+    const int nv = (a.N + 31) / 32;
+    const int es = dtype == TB_BF16 ? 2 : 4;
+    const int chn = a.heads * a.P + 2 * a.groups * a.N;
+    const bool vec8 = a.N % 8 == 0 && ((size_t)chn * es) % 16 == 0 && ((size_t)a.heads * a.P * es) % 16 == 0 &&
+                      ((uintptr_t)a.xbc & 15) == 0;
+#define SCAN2(NV_, PT_) do { \
+        const size_t smem = (size_t)(SCAN_TT * 2 * (NV_) * 32 + SCAN_TT * (PT_) + SCAN_TT * 2) * sizeof(float); \
+        if (vec8) DISPATCH2(dtype, w_dtype, tb_launch(mamba2_scan_kernel<T, TW, NV_, PT_, true>, dim3(grid), dim3(SCAN_NS * (PT_) / SCAN_PP), smem, stream, a)); \
+        else DISPATCH2(dtype, w_dtype, tb_launch(mamba2_scan_kernel<T, TW, NV_, PT_, false>, dim3(grid), dim3(SCAN_NS * (PT_) / SCAN_PP), smem, stream, a)); \
+    } while (0)
+#define SCAN(NV_) do { if (pt == 32) SCAN2(NV_, 32); else SCAN2(NV_, 16); } while (0)
+    if (nv <= 1) SCAN(1); else if (nv <= 2) SCAN(2); else if (nv <= 4) SCAN(4); else SCAN(8);
 #undef SCAN
+#undef SCAN2
     return tb_launch_status();
 }
 

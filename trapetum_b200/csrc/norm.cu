@@ -481,7 +481,7 @@ extern "C" int tb_residual_add(float* h, const void* a, int a_dtype, long long n
 //
 // `a` may be split-K partial sums, added in split order.  One CTA per row, the row's sums kept in shared memory
 // between the two passes when they fit.  Everything is 32-bit.
-template <typename TA, typename TW, typename TO, bool POST>
+template <typename TA, typename TW, typename TO, bool POST, int VEC>
 __global__ void fold_rmsnorm_kernel(float* __restrict__ h, float alpha, const TA* __restrict__ a, int n_splits,
                                     long long split_stride, const TW* __restrict__ w, float eps, float offset,
                                     TO* __restrict__ out, int width, int row_cache) {
@@ -490,27 +490,43 @@ __global__ void fold_rmsnorm_kernel(float* __restrict__ h, float alpha, const TA
     extern __shared__ __align__(16) float row[];
     __shared__ float red[33];
     const size_t base = (size_t)blockIdx.x * width;
+    const int step = blockDim.x * VEC;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v[1];
-        load_sum<TA, 1>(a + base + i, n_splits, split_stride, v);
-        if (POST) v[0] = alpha * h[base + i] + v[0];
-        if (row_cache) row[i] = v[0];
-        ss += v[0] * v[0];
+    for (int i = threadIdx.x * VEC; i < width; i += step) {
+        float v[VEC], hv[VEC];
+        load_sum<TA, VEC>(a + base + i, n_splits, split_stride, v);
+        if (POST) {
+            if (VEC == 4) Vec4<float>::load(h + base + i, hv); else hv[0] = h[base + i];
+#pragma unroll
+            for (int e = 0; e < VEC; e++) v[e] = alpha * hv[e] + v[e];
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; e++) { if (row_cache) row[i + e] = v[e]; ss += v[e] * v[e]; }
     }
     ss = block_sum(ss, red);
     const float r = 1.0f / sqrtf(ss / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v[1];
-        if (row_cache) v[0] = row[i];
-        else {
-            load_sum<TA, 1>(a + base + i, n_splits, split_stride, v);
-            if (POST) v[0] = alpha * h[base + i] + v[0];
+    for (int i = threadIdx.x * VEC; i < width; i += step) {
+        float v[VEC], hv[VEC], g[VEC];
+        const bool need_h = !POST || !row_cache;
+        if (need_h) { if (VEC == 4) Vec4<float>::load(h + base + i, hv); else hv[0] = h[base + i]; }
+        if (row_cache) {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) v[e] = row[i + e];
+        } else {
+            load_sum<TA, VEC>(a + base + i, n_splits, split_stride, v);
+            if (POST) {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) v[e] = alpha * hv[e] + v[e];
+            }
         }
-        const float y = v[0] * r * (offset + to_f<TW>(w[i]));
-        const float hn = POST ? y : h[base + i] + y;
-        h[base + i] = hn;
-        if (out != nullptr) out[base + i] = from_f<TO>(hn);
+        if (VEC == 4) Vec4<TW>::load(w + i, g); else g[0] = to_f<TW>(w[i]);
+#pragma unroll
+        for (int e = 0; e < VEC; e++) {
+            const float y = v[e] * r * (offset + g[e]);
+            v[e] = POST ? y : hv[e] + y;
+        }
+        if (VEC == 4) Vec4<float>::store(h + base + i, v); else h[base + i] = v[0];
+        if (out != nullptr) { if (VEC == 4) Vec4<TO>::store(out + base + i, v); else out[base + i] = from_f<TO>(v[0]); }
     }
 }
 
@@ -525,15 +541,14 @@ extern "C" int tb_fold_rmsnorm(float* h, int post, float alpha, const void* a, i
     if (n_splits < 1) return tb_refuse("fold_rmsnorm: n_splits=%d", n_splits);
     const int row_cache = (size_t)width * sizeof(float) <= 40 * 1024;
     const size_t smem = row_cache ? (size_t)width * sizeof(float) : 0;
-    const int threads = norm_threads(width, 1);
-    if (post)
-        DISPATCH3(a_dtype, w_dtype, out_dtype,
-            tb_launch(fold_rmsnorm_kernel<TX, TW, TO, true>, dim3(rows), dim3(threads), smem, stream,
-                h, alpha, (const TX*)a, n_splits, split_stride, (const TW*)w, eps, offset, (TO*)out, width, row_cache));
-    else
-        DISPATCH3(a_dtype, w_dtype, out_dtype,
-            tb_launch(fold_rmsnorm_kernel<TX, TW, TO, false>, dim3(rows), dim3(threads), smem, stream,
-                h, alpha, (const TX*)a, n_splits, split_stride, (const TW*)w, eps, offset, (TO*)out, width, row_cache));
+    const bool vec = width % 4 == 0 && split_stride % 4 == 0 && aligned16(h) && aligned16(a) && aligned16(w) && aligned16(out);
+#define FOLD(POST_, VEC_)                                                                                          \
+        DISPATCH3(a_dtype, w_dtype, out_dtype,                                                                     \
+            tb_launch(fold_rmsnorm_kernel<TX, TW, TO, POST_, VEC_>, dim3(rows), dim3(norm_threads(width, VEC_)), smem, stream, \
+                h, alpha, (const TX*)a, n_splits, split_stride, (const TW*)w, eps, offset, (TO*)out, width, row_cache))
+    if (post) { if (vec) FOLD(true, 4); else FOLD(true, 1); }
+    else { if (vec) FOLD(false, 4); else FOLD(false, 1); }
+#undef FOLD
     return tb_launch_status();
 }
 

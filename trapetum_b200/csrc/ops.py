@@ -245,8 +245,10 @@ def gated_act(gu: torch.Tensor, activation: str, out_dtype: torch.dtype, limit: 
     return out
 
 
-def token_gate(g: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, col0: int) -> torch.Tensor:
-    """out[t, j] = gelu_tanh(g[t, j]) * table[ids[t], col0 + j], in g's dtype (the product 32-bit)."""
+def token_gate(g: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, col0: int,
+               out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """out[t, j] = gelu_tanh(g[t, j]) * table[ids[t], col0 + j], computed in 32-bit, stored in ``out_dtype``
+    (default: g's dtype)."""
     _cuda(g, ids, table)
     if g.dim() != 2 or not g.is_contiguous():
         raise KernelError("token_gate: g must be contiguous [tokens, dim]")
@@ -254,22 +256,12 @@ def token_gate(g: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, col0: in
         raise KernelError("token_gate: ids must be contiguous int32 [tokens]")
     if table.dim() != 2 or table.stride(1) != 1 or col0 < 0 or col0 + g.shape[1] > table.shape[1]:
         raise KernelError(f"token_gate: columns {col0}..{col0 + g.shape[1]} do not lie in a table of shape {tuple(table.shape)}")
-    out = torch.empty_like(g)
+    out = torch.empty(g.shape, dtype=out_dtype or g.dtype, device=g.device)
     lib = build.load("activation")
     _check(lib, lib.tb_token_gate(_ptr(g), c_int(code(g.dtype)), _ptr(ids), _ptr(table), c_int(code(table.dtype)),
                                   c_longlong(table.stride(0)), c_int(col0), c_int(table.shape[0]), _ptr(out),
-                                  c_int(g.shape[0]), c_int(g.shape[1]), _stream()), "token_gate")
+                                  c_int(code(out.dtype)), c_int(g.shape[0]), c_int(g.shape[1]), _stream()), "token_gate")
     return out
-
-
-def scale_(x: torch.Tensor, s: float) -> torch.Tensor:
-    """x *= s in place (float32)."""
-    _cuda(x)
-    if x.dtype != torch.float32 or not x.is_contiguous():
-        raise KernelError("scale_: wants a contiguous float32 tensor")
-    lib = build.load("activation")
-    _check(lib, lib.tb_scale(_ptr(x), c_float(s), c_longlong(x.numel()), _stream()), "scale")
-    return x
 
 
 def add_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
@@ -286,8 +278,8 @@ def add_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
 
 # ---------------------------------------------------------------------------
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: float = 0.0,
-              out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """a[M,K] @ w[N,K]^T with 32-bit FMA (no tensor cores)."""
+              out: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> torch.Tensor:
+    """a[M,K] @ w[N,K]^T with 32-bit FMA (no tensor cores); the result times ``out_scale`` (after the cap)."""
     _cuda(a, w, out)
     _rows_contig(a, "gemm: a")
     _rows_contig(w, "gemm: w")
@@ -300,10 +292,10 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap:
     else:
         _rows_contig(out, "gemm: out")
     lib = build.load("gemm_simt")
-    _check(lib, lib.tb_gemm_simt(_ptr(a), c_int(code(a.dtype)), _ptr(w), c_int(code(w.dtype)), _ptr(out),
-                                 c_int(code(out.dtype)), c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)),
-                                 c_longlong(w.stride(0)), c_longlong(out.stride(0)), c_float(softcap or 0.0),
-                                 _stream()), "gemm_simt")
+    _check(lib, lib.tb_gemm_simt_ex(_ptr(a), c_int(code(a.dtype)), _ptr(w), c_int(code(w.dtype)), _ptr(out),
+                                    c_int(code(out.dtype)), c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)),
+                                    c_longlong(w.stride(0)), c_longlong(out.stride(0)), c_float(softcap or 0.0),
+                                    c_float(out_scale), _stream()), "gemm_simt")
     return out
 
 
@@ -422,7 +414,7 @@ def headnorm_kv(partial: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: 
 
 
 class _Mamba2Args(ctypes.Structure):
-    _fields_ = [("proj", c_void_p), ("proj_stride", c_longlong),
+    _fields_ = [("proj", c_void_p), ("proj_stride", c_longlong), ("dt", c_void_p), ("dt_stride", c_longlong),
                 ("heads", c_int), ("P", c_int), ("N", c_int), ("groups", c_int), ("taps", c_int), ("norm_groups", c_int),
                 ("conv_w", c_void_p), ("conv_b", c_void_p), ("dt_bias", c_void_p), ("A_log", c_void_p), ("D", c_void_p),
                 ("norm_w", c_void_p), ("eps", c_float),
@@ -436,19 +428,21 @@ def mamba2_state_size(heads: int, P: int, N: int, groups: int, taps: int) -> int
     return heads * P * N + (taps - 1) * (heads * P + 2 * groups * N)
 
 
-def mamba2(proj: torch.Tensor, heads: int, P: int, N: int, groups: int, taps: int, norm_groups: int,
+def mamba2(proj: torch.Tensor, dt_raw: torch.Tensor, heads: int, P: int, N: int, groups: int, taps: int, norm_groups: int,
            conv_w: torch.Tensor, conv_b: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor,
            norm_w: torch.Tensor, eps: float, state: torch.Tensor, seq_start: torch.Tensor, token_seq: torch.Tensor,
            slot_ids: torch.Tensor, batch: int, one_token_each: bool) -> torch.Tensor:
     """Everything of the state-space mixer between its two products (see mamba2.cu): from the input product's rows
-    ``proj`` [T, inner + channels + heads] to the gated, normed [T, inner] that the output product reads, with the
-    sequences' states (``state`` [slots, mamba2_state_size] float32, rows picked by ``slot_ids``) carried along."""
-    _cuda(proj, conv_w, conv_b, dt_bias, A_log, D, norm_w, state, seq_start, token_seq, slot_ids)
+    ``proj`` [T, inner + channels] (compute dtype) and step sizes ``dt_raw`` [T, heads] (float32, before bias and
+    softplus) to the gated, normed [T, inner] that the output product reads, with the sequences' states (``state`` [slots, mamba2_state_size] float32, rows picked by ``slot_ids``) carried along."""
+    _cuda(proj, dt_raw, conv_w, conv_b, dt_bias, A_log, D, norm_w, state, seq_start, token_seq, slot_ids)
     inner, ch = heads * P, heads * P + 2 * groups * N
     _rows_contig(proj, "mamba2: proj")
     T = proj.shape[0]
-    if proj.shape[1] != inner + ch + heads:
-        raise KernelError(f"mamba2: the input product has {proj.shape[1]} columns, the sizes ask for {inner + ch + heads}")
+    if proj.shape[1] != inner + ch:
+        raise KernelError(f"mamba2: the input product has {proj.shape[1]} columns, the sizes ask for {inner + ch}")
+    if dt_raw.dtype != torch.float32 or tuple(dt_raw.shape) != (T, heads) or dt_raw.stride(1) != 1:
+        raise KernelError(f"mamba2: the step sizes must be float32 [{T}, {heads}], got {tuple(dt_raw.shape)} {dt_raw.dtype}")
     wd = conv_w.dtype
     for name, t, shape in (("conv", conv_w, (ch, taps)), ("conv bias", conv_b, (ch,)), ("dt_bias", dt_bias, (heads,)),
                            ("A_log", A_log, (heads,)), ("D", D, (heads,)), ("norm", norm_w, (inner,))):
@@ -463,6 +457,7 @@ def mamba2(proj: torch.Tensor, heads: int, P: int, N: int, groups: int, taps: in
     out = torch.empty((T, inner), dtype=dt, device=proj.device)
     a = _Mamba2Args()
     a.proj = proj.data_ptr(); a.proj_stride = proj.stride(0)
+    a.dt = dt_raw.data_ptr(); a.dt_stride = dt_raw.stride(0)
     a.heads = heads; a.P = P; a.N = N; a.groups = groups; a.taps = taps; a.norm_groups = norm_groups
     a.conv_w = conv_w.data_ptr(); a.conv_b = conv_b.data_ptr(); a.dt_bias = dt_bias.data_ptr()
     a.A_log = A_log.data_ptr(); a.D = D.data_ptr(); a.norm_w = norm_w.data_ptr(); a.eps = eps
@@ -628,7 +623,7 @@ def gemm_tc_takes(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-GEMM_TC_GATES = ("gelu_tanh", "silu")
+GEMM_TC_GATES = ("gelu_tanh", "silu", "clamped_swish")
 
 
 def gemm_tc_gates(activation: str) -> bool:
@@ -638,14 +633,15 @@ def gemm_tc_gates(activation: str) -> bool:
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: float = 0.0,
             splits: Optional[int] = None, out: Optional[torch.Tensor] = None, partials: bool = False,
-            gated_act: Optional[str] = None, act_limit: float = 0.0) -> torch.Tensor:
+            gated_act: Optional[str] = None, act_limit: float = 0.0, out_scale: float = 1.0) -> torch.Tensor:
     """a[M,K] @ w[N,K]^T in bfloat16 on tcgen05 tensor cores with 32-bit accumulation.
     ``splits`` None: the library picks the K split (more than 1 only for few tokens and few weight rows).
     ``partials=True`` returns float32 [splits, M, N] whose sum over the first axis, taken in order, is the
     product: a consumer that reads the product once anyway adds them on the way and saves a pass.
     ``gated_act`` ("gelu_tanh" or "silu"): ``w`` holds gate and up rows interleaved in blocks of 16
     (see :func:`interleave_gate_up`); the result is bfloat16 [M, N/2] = act(gate) * up, taken on the
-    32-bit accumulators in the epilogue."""
+    32-bit accumulators in the epilogue ("clamped_swish" takes ``act_limit``).  ``out_scale``: the result times this
+    number (not with a cap, a gate or partial sums)."""
     _cuda(a, w, out)
     if not gemm_tc_takes(a, w):
         raise KernelError(f"gemm_tc does not take a {tuple(a.shape)}/{a.stride()} {a.dtype}, "
@@ -659,17 +655,17 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: f
     if gated_act is not None:
         if not gemm_tc_gates(gated_act):
             raise KernelError(f"gemm_tc: the epilogue does not know activation '{gated_act}' (known: {GEMM_TC_GATES})")
-        if N % 32 or partials or softcap:
-            raise KernelError("gemm_tc: the gated epilogue needs a multiple of 32 weight rows, no partials, no cap")
+        if N % 32 or partials or softcap or out_scale != 1.0:
+            raise KernelError("gemm_tc: the gated epilogue needs a multiple of 32 weight rows, no partials, no cap, no scale")
         out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)
-        _check(lib, lib.tb_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(1), c_int(M), c_int(N), c_int(K),
-                                   c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
-                                   c_float(0.0), c_int(1), _ptr(None), c_int(1), c_int(ACTIVATIONS[gated_act]),
-                                   _stream()), "gemm_tc")
+        _check(lib, lib.tb_gemm_tc_ex(_ptr(a), _ptr(w), _ptr(out), c_int(1), c_int(M), c_int(N), c_int(K),
+                                      c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
+                                      c_float(0.0), c_int(1), _ptr(None), c_int(1), c_int(ACTIVATIONS[gated_act]),
+                                      c_float(act_limit), c_float(1.0), _stream()), "gemm_tc")
         return out
     if partials:
-        if softcap:
-            raise KernelError("gemm_tc: a soft cap cannot be applied to partial sums")
+        if softcap or out_scale != 1.0:
+            raise KernelError("gemm_tc: neither a soft cap nor a scale can be applied to partial sums")
         part = torch.empty((splits, M, N), dtype=torch.float32, device=a.device)
         if splits == 1:
             _check(lib, lib.tb_gemm_tc(_ptr(a), _ptr(w), _ptr(part), c_int(0), c_int(M), c_int(N), c_int(K),
@@ -687,9 +683,10 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: f
     scratch = None
     if splits > 1:
         scratch = torch.empty(splits * M * N, dtype=torch.float32, device=a.device)
-    _check(lib, lib.tb_gemm_tc(_ptr(a), _ptr(w), _ptr(out), c_int(code(out.dtype)), c_int(M), c_int(N), c_int(K),
-                               c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
-                               c_float(softcap or 0.0), c_int(splits), _ptr(scratch), c_int(1), c_int(-1), _stream()), "gemm_tc",
+    _check(lib, lib.tb_gemm_tc_ex(_ptr(a), _ptr(w), _ptr(out), c_int(code(out.dtype)), c_int(M), c_int(N), c_int(K),
+                                  c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
+                                  c_float(softcap or 0.0), c_int(splits), _ptr(scratch), c_int(1), c_int(-1),
+                                  c_float(0.0), c_float(out_scale), _stream()), "gemm_tc",
            2 if splits > 1 else 1)
     return out
 

@@ -64,11 +64,10 @@ class LinearHead(Part):
         self.weight = own if own is not None else tensors[self.prefix + self.tied_to]
 
     def kernel_files(self):
-        return linear_kernels(self.rt.dtype) + (("activation",) if self.scale != 1.0 else ())
+        return linear_kernels(self.rt.dtype)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        logits = linear(x, self.weight, torch.float32, self.softcap)
-        return ops.scale_(logits, self.scale) if self.scale != 1.0 else logits
+        return linear(x, self.weight, torch.float32, self.softcap, self.scale)
 
 
 register_part("embedding", "embedding", Embedding)

@@ -69,7 +69,8 @@ class GatedMLP(FeedForward):
         if self.fused:
             raise RuntimeError("gated_mlp: the interleaved weights need the tensor-core product, which does not take "
                                f"an input of shape {tuple(x.shape)} with strides {x.stride()}")
-        gu = linear(x, self.w_gu, self.rt.dtype)
+        # an activation with thresholds gets its inputs unrounded, as the fused epilogue gives them
+        gu = linear(x, self.w_gu, torch.float32 if self.limit else self.rt.dtype)
         act = ops.gated_act(gu, self.activation, self.rt.dtype, self.limit)
         return linear_partials(act, self.w_down)
 
@@ -119,8 +120,8 @@ class TokenGated(FeedForward):
     def forward(self, x, ctx):
         if ctx.token_ids is None:
             raise RuntimeError("token_gated: the step's context carries no token ids")
-        g = linear(x, self.w_gate, self.rt.dtype)
-        return linear_partials(ops.token_gate(g, ctx.token_ids, self.table, self.first_col), self.w_proj)
+        g = linear(x, self.w_gate, torch.float32)          # narrow: kept 32-bit up to the activation
+        return linear_partials(ops.token_gate(g, ctx.token_ids, self.table, self.first_col, self.rt.dtype), self.w_proj)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

@@ -14,11 +14,13 @@ import torch
 from ..csrc import ops
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: Optional[float] = None) -> torch.Tensor:
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: Optional[float] = None,
+           scale: float = 1.0) -> torch.Tensor:
+    """``scale``: the product times this number, in the kernel's epilogue (after the cap, if both are given)."""
     cap = float(softcap) if softcap else 0.0
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ops.gemm_tc_takes(x, w):
-        return ops.gemm_tc(x, w, out_dtype, cap)
-    return ops.gemm_simt(x, w, out_dtype, cap)
+        return ops.gemm_tc(x, w, out_dtype, cap, out_scale=scale)
+    return ops.gemm_simt(x, w, out_dtype, cap, out_scale=scale)
 
 
 def linear_partials(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:

@@ -10,8 +10,9 @@ groups * state columns of B and of C, one dt per head) and an output product ``W
 * ``y * silu(z)`` is RMS-normed in ``norm_groups`` equal parts (the gate before the norm), times a weight.
 
 A sequence's state (S and the last ``conv - 1`` convolution inputs) is one float32 row of the cache's state
-area, addressed by slot, zero when the sequence starts.  Softplus, the decay, the state, y and the gated norm
-are 32-bit; the products and the convolution with its silu work in the compute dtype.  The kernels are in
+area, addressed by slot, zero when the sequence starts.  The step sizes (they enter an exponential), softplus,
+the decay, the state, y and the gated norm are 32-bit: dt comes from a product of its own with 32-bit output.
+The other products and the convolution with its silu work in the compute dtype.  The kernels are in
 ``csrc/mamba2.cu``; a step of one token per sequence and a step of whole prompts use the same recurrence.
 
 Parameters (none is fixed in code): ``hidden_size``, ``heads``, ``head_dim``, ``state``, ``groups``, ``conv``,
@@ -68,7 +69,9 @@ class Mamba2(Mixer):
         }
 
     def bind(self, tensors) -> None:
-        self.w_in = tensors[self._name("in")]
+        w_in = tensors[self._name("in")]
+        self.w_in = w_in[:self.inner + self.channels]             # z, x, B, C: output in the compute dtype
+        self.w_dt = w_in[self.inner + self.channels:]             # dt: output in 32-bit
         self.w_o = tensors[self._name("o")]
         # the small tensors enter 32-bit arithmetic: kept in 32 bits (exact for what a file stores in 16)
         self.w = {k: tensors[self._name(k)].float().contiguous()
@@ -82,8 +85,9 @@ class Mamba2(Mixer):
 
     def forward(self, x, ctx, state):
         proj = linear(x, self.w_in, self.rt.dtype)
+        dt_raw = linear(x, self.w_dt, torch.float32)
         w = self.w
-        y = ops.mamba2(proj, self.heads, self.P, self.N, self.groups, self.taps, self.norm_groups, w["conv_w"],
+        y = ops.mamba2(proj, dt_raw, self.heads, self.P, self.N, self.groups, self.taps, self.norm_groups, w["conv_w"],
                        w["conv_b"], w["dt_bias"], w["A_log"], w["D"], w["norm"], self.eps, state.data, ctx.seq_start,
                        ctx.token_seq, ctx.slot_ids, ctx.batch, one_token_each=not ctx.is_prefill)
         return linear_partials(y, self.w_o)
