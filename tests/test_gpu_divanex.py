@@ -93,16 +93,17 @@ def test_head_norm_temperature_and_cache_write(H, G, d, every, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("lens", [[37, 1, 18], [530, 1, 300]])
 @pytest.mark.parametrize("heads, P, N, groups, taps, ngroups", [(2, 16, 8, 2, 3, 2), (3, 24, 20, 1, 2, 3), (4, 32, 64, 2, 4, 1),
                                                                 (1, 8, 130, 1, 1, 1), (2, 40, 16, 1, 6, 4)])
-def test_state_space_mixer_between_its_products(heads, P, N, groups, taps, ngroups, dtype):
+def test_state_space_mixer_between_its_products(heads, P, N, groups, taps, ngroups, lens, dtype):
     """Convolution, recurrence and gated norm: prompts of unequal lengths in slots that are not in order, then three
-    single tokens each, against the oracle's functions; the state is carried by the kernels."""
+    single tokens each, against the oracle's functions; the state is carried by the kernels.  The long prompts are cut
+    into chunks that run side by side (the short one beside them is a single chunk)."""
     from trapetum_b200.csrc import ops
     dt = DTYPES[dtype]
     g = torch.Generator().manual_seed(heads * 100 + N)
     inner, ch = heads * P, heads * P + 2 * groups * N
-    lens = [37, 1, 18]
     slots = torch.tensor([4, 0, 2]).int()
     rn = lambda *s: torch.randn(*s, generator=g)
     wts = {"conv": rn(ch, taps) * 0.5, "conv.b": rn(ch) * 0.2, "dt_bias": rn(heads) - 1.0, "A_log": torch.rand(heads, generator=g) * 2 - 1.5,
@@ -138,7 +139,7 @@ def test_state_space_mixer_between_its_products(heads, P, N, groups, taps, ngrou
         token_seq = torch.repeat_interleave(torch.arange(len(step_lens)), torch.tensor(step_lens)).int().to(DEV)
         return ops.mamba2(rows[:, :inner + ch].to(DEV).to(dt), rows[:, inner + ch:].to(DEV).contiguous(), heads, P, N, groups, taps, ngroups, dev["conv"], dev["conv.b"], dev["dt_bias"],
                           dev["A_log"], dev["D"], dev["norm"], eps, state, seq_start, token_seq, slots.to(DEV), len(step_lens),
-                          one_each)
+                          one_each, max_seq_len=0 if one_each else max(step_lens))
 
     tol = 2e-5 if dtype == "float32" else 3e-2
     for step in range(4):
@@ -153,6 +154,10 @@ def test_state_space_mixer_between_its_products(heads, P, N, groups, taps, ngrou
             err = float((got[at:at + n] - want).norm() / want.norm())
             assert err <= tol, f"step {step}, sequence {b}: {err:.3e}"
             at += n
+    if max(lens) >= 256:
+        chunk_len = __import__("ctypes").c_int(0)
+        from trapetum_b200.csrc import build
+        assert build.load("mamba2").tb_mamba2_plan(heads, P, len(lens), max(lens), __import__("ctypes").byref(chunk_len)) > 1
     assert bool((state[1] == 7.0).all()) and bool((state[3] == 0).all()) and bool((state[5] == 0).all())
     S = state[4, :heads * P * N].view(heads, P, N).double().cpu()
     assert float((S - ost[0]["S"].transpose(1, 2)).norm() / ost[0]["S"].norm()) <= tol

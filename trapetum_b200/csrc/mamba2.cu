@@ -10,7 +10,12 @@
 //   tb_mamba2_scan       per head h (group g = h / (heads / groups)), with dt = softplus(dt_raw + dt_bias):
 //                          S <- exp(-exp(A_log[h]) dt) S + dt * x_t B_t^T      S is [P][N]
 //                          y_t = S C_t + D[h] x_t
-//                        sequential over a sequence's tokens, S read from and written back to the state.
+//                        sequential over a sequence's tokens, S read from and written back to the state.  Where few
+//                        long prompts would leave most SMs idle, a prompt is cut into chunks: one launch runs the
+//                        recurrence of every chunk but the last from zero and keeps its end state and the product of
+//                        its decays, a second launch starts every chunk from what the chunks before it left
+//                        (S_c = D_(c-1) S_(c-1) + E_(c-1), folded by the chunk itself) and writes y.  Twice the
+//                        arithmetic, chunks times the parallelism; the same sums in another order.
 //   tb_mamba2_gate_norm  out = groupnorm(y * silu(z)) * w, the norm over `norm_groups` equal parts of a row.
 //
 // The state of a sequence is one 32-bit row: [heads][P][N] of S, then [taps-1][channels] of conv inputs
@@ -37,6 +42,9 @@ struct Mamba2Args {
     float* y;                                      // [tokens][inner]
     void* out;                                     // [tokens][inner], compute dtype
     int batch, n_tokens;
+    // a long prompt cut into chunks that run side by side (see mamba2_scan_kernel): end states [batch][n_chunks][heads*P*N],
+    // decay products [batch][n_chunks][heads], tokens per chunk (a multiple of the tile), chunks per sequence
+    float* chunk_state; float* chunk_decay; int chunk_len; int n_chunks;
 };
 
 // ---------------------------------------------------------------------------------------------------------
@@ -141,7 +149,11 @@ template <> struct Chunk8<float> {
 };
 
 // VEC8: N is a multiple of 8 and the rows of B and C start on 16-byte boundaries.
-template <typename T, typename TW, int NV, int PT, bool VEC8>
+// MODE 0: a whole sequence per CTA.  MODE 1: a chunk from zero (the first chunk: from the sequence's state, of which it
+// also leaves a copy in the last chunk's slot, which is otherwise unused), end state and decay product kept, no y;
+// the last chunk of a sequence does nothing.  MODE 2: a chunk from the folded states of the chunks before it, y
+// written; the last chunk writes the sequence's state (only it reads it in this launch: a sequence of one chunk).
+template <typename T, typename TW, int NV, int PT, bool VEC8, int MODE>
 __global__ void __launch_bounds__(SCAN_NS * PT / SCAN_PP) mamba2_scan_kernel(Mamba2Args a) {
     pdl_launch_dependents();
     constexpr int NP = NV * 32;                                      // padded state size (zeros beyond N)
@@ -152,7 +164,8 @@ __global__ void __launch_bounds__(SCAN_NS * PT / SCAN_PP) mamba2_scan_kernel(Mam
     extern __shared__ __align__(16) float sh[];                      // [TT][NP] B, [TT][NP] C, [TT][PT] x, [TT][2] dt and decay
     const int N = a.N, P = a.P, H = a.heads;
     const int inner = H * P, ch = inner + 2 * a.groups * N;
-    const int b = blockIdx.z, h = blockIdx.y, p0 = blockIdx.x * PT;
+    const int b = MODE == 0 ? blockIdx.z : blockIdx.z / a.n_chunks, chunk = MODE == 0 ? 0 : blockIdx.z % a.n_chunks;
+    const int h = blockIdx.y, p0 = blockIdx.x * PT;
     const int g = h / (H / a.groups);
     const int ns = threadIdx.x % SCAN_NS, pl = threadIdx.x / SCAN_NS;
     const int p = p0 + pl * SCAN_PP;                                 // this thread's first p
@@ -164,18 +177,51 @@ __global__ void __launch_bounds__(SCAN_NS * PT / SCAN_PP) mamba2_scan_kernel(Mam
     const float Dh = to_f<TW>(((const TW*)a.D)[h]);
     const float dtb = to_f<TW>(((const TW*)a.dt_bias)[h]);
     pdl_wait();
-    const int s0 = a.seq_start[b], s1 = a.seq_start[b + 1];
+    int s0 = a.seq_start[b], s1 = a.seq_start[b + 1];
+    bool last = true;
+    if (MODE != 0) {                                                 // this CTA's chunk of the sequence
+        const int end = s1;
+        s0 += chunk * a.chunk_len;
+        if (s0 >= end) return;                                       // (the same in every thread)
+        s1 = min(end, s0 + a.chunk_len);
+        last = s1 == end;
+        if (MODE == 1 && last) return;
+    }
     float* S = a.state + (size_t)a.slot_ids[b] * a.state_stride + (size_t)h * P * N;
+    const size_t hpn = (size_t)H * P * N;
+    float* E = MODE == 0 ? nullptr : a.chunk_state + (size_t)b * a.n_chunks * hpn + (size_t)h * P * N;   // chunk 0's slot, this head
     float s[SCAN_PP][NV][4];
+    auto each = [&](auto&& f) {                                      // f(j, k, e, offset in [P][N]) for the states this thread owns
+#pragma unroll
+        for (int j = 0; j < SCAN_PP; j++)
+#pragma unroll
+            for (int k = 0; k < NV; k++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int n = (k * SCAN_NS + ns) * 4 + e;
+                    if (p + j < P && n < N) f(j, k, e, (size_t)(p + j) * N + n);
+                }
+    };
 #pragma unroll
     for (int j = 0; j < SCAN_PP; j++)
 #pragma unroll
         for (int k = 0; k < NV; k++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int n = (k * SCAN_NS + ns) * 4 + e;
-                s[j][k][e] = (p + j < P && n < N) ? S[(size_t)(p + j) * N + n] : 0.f;
-            }
+            for (int e = 0; e < 4; e++) s[j][k][e] = 0.f;
+    if (MODE == 0 || (MODE == 2 && chunk == 0 && last)) {
+        each([&](int j, int k, int e, size_t o) { s[j][k][e] = S[o]; });
+    } else if (MODE == 1) {
+        if (chunk == 0) each([&](int j, int k, int e, size_t o) { s[j][k][e] = S[o]; E[(size_t)(a.n_chunks - 1) * hpn + o] = S[o]; });
+    } else if (chunk == 0) {
+        each([&](int j, int k, int e, size_t o) { s[j][k][e] = E[(size_t)(a.n_chunks - 1) * hpn + o]; });
+    } else {
+        for (int c = 0; c < chunk; c++) {                            // the first chunk's end state holds the sequence's state already
+            const float d = c == 0 ? 0.f : a.chunk_decay[((size_t)b * a.n_chunks + c) * H + h];
+            const float* Ec = E + (size_t)c * hpn;
+            each([&](int j, int k, int e, size_t o) { s[j][k][e] = d * s[j][k][e] + Ec[o]; });
+        }
+    }
+    float decay = 1.f;
     const T* xbc = (const T*)a.xbc;
 
     Chunk8<T> pre[VEC8 ? CPT : 1];
@@ -240,6 +286,7 @@ __global__ void __launch_bounds__(SCAN_NS * PT / SCAN_PP) mamba2_scan_kernel(Mam
             yp[2 * tt] = yp[2 * tt + 1] = 0.f;
             if (tt < nt) {                                           // the same in every thread of the CTA
                 const float dec = sdt[2 * tt + 1], dt = sdt[2 * tt];
+                if (MODE == 1) decay *= dec;
                 const float dx0 = dt * sx[tt * PT + pl * SCAN_PP], dx1 = dt * sx[tt * PT + pl * SCAN_PP + 1];
                 const float4* Bt = (const float4*)(sB + tt * NP);
                 const float4* Ct = (const float4*)(sC + tt * NP);
@@ -258,6 +305,7 @@ __global__ void __launch_bounds__(SCAN_NS * PT / SCAN_PP) mamba2_scan_kernel(Mam
                 yp[2 * tt + 1] = (y1[0] + y1[1]) + (y1[2] + y1[3]);
             }
         }
+        if (MODE != 1) {                                             // (end states only: no outputs)
         // the eight threads of a pair add their parts: at each stage a thread keeps one half of its values and hands
         // the other to its partner; thread ns ends with the sums of tokens 2 ns and 2 ns + 1, both p
 #pragma unroll
@@ -278,18 +326,14 @@ __global__ void __launch_bounds__(SCAN_NS * PT / SCAN_PP) mamba2_scan_kernel(Mam
             if (tt < nt && p + j < P)
                 a.y[(size_t)(tb + tt) * inner + h * P + p + j] = yp[r] + Dh * sx[tt * PT + pl * SCAN_PP + j];
         }
-    }
-#pragma unroll
-    for (int j = 0; j < SCAN_PP; j++)
-        if (p + j < P) {
-#pragma unroll
-            for (int k = 0; k < NV; k++)
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int n = (k * SCAN_NS + ns) * 4 + e;
-                    if (n < N) S[(size_t)(p + j) * N + n] = s[j][k][e];
-                }
         }
+    }
+    if (MODE == 1) {
+        each([&](int j, int k, int e, size_t o) { E[(size_t)chunk * hpn + o] = s[j][k][e]; });
+        if (blockIdx.x == 0 && threadIdx.x == 0) a.chunk_decay[((size_t)b * a.n_chunks + chunk) * H + h] = decay;
+    } else if (last) {
+        each([&](int j, int k, int e, size_t o) { S[o] = s[j][k][e]; });
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -358,34 +402,74 @@ extern "C" int tb_mamba2_conv(const Mamba2Args* args, int dtype, int w_dtype, in
     return tb_launch_status();
 }
 
-extern "C" int tb_mamba2_scan(const Mamba2Args* args, int dtype, int w_dtype, cudaStream_t stream) {
-    Mamba2Args a = *args;
-    if (a.n_tokens <= 0) return 0;
-    if (check(a)) return -1;
+static int scan_sms() {
     static int sms = 0;
     if (!sms) {
         int dev = 0; cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
     }
+    return sms;
+}
+
+// Into how many chunks (and of how many tokens) the longest prompt of a step is cut: 1 unless the (sequence, head,
+// 32 values of P) tiles are fewer than four an SM and the prompt is long enough for chunks of 128 tokens and more.
+extern "C" int tb_mamba2_plan(int heads, int P, int batch, int max_seq_len, int* chunk_len) {
+    const long long tiles = (long long)((P + 31) / 32) * heads * batch;
+    const int sms = scan_sms();
+    int chunks = 1;
+    if (tiles < 4LL * sms && max_seq_len >= 256) {
+        chunks = (int)((6LL * sms + tiles - 1) / tiles);
+        if (chunks > max_seq_len / 128) chunks = max_seq_len / 128;
+        if (chunks > 64) chunks = 64;
+    }
+    int len = (max_seq_len + chunks - 1) / chunks;
+    len = (len + SCAN_TT - 1) / SCAN_TT * SCAN_TT;
+    if (len < SCAN_TT) len = SCAN_TT;
+    chunks = (max_seq_len + len - 1) / len;
+    if (chunks < 1) chunks = 1;
+    if (chunk_len) *chunk_len = len;
+    return chunks;
+}
+
+extern "C" int tb_mamba2_scan(const Mamba2Args* args, int dtype, int w_dtype, cudaStream_t stream) {
+    Mamba2Args a = *args;
+    if (a.n_tokens <= 0) return 0;
+    if (check(a)) return -1;
+    const int sms = scan_sms();
+    const bool chunked = a.n_chunks > 1;
+    if (chunked && (a.chunk_state == nullptr || a.chunk_decay == nullptr || a.chunk_len < SCAN_TT || a.chunk_len % SCAN_TT))
+        return tb_refuse("mamba2: chunks need their scratch and a length that is a multiple of %d", SCAN_TT);
+    const int zdim = a.batch * (chunked ? a.n_chunks : 1);
     // thirty-two values of P a CTA (128 threads), or sixteen where that would leave SMs without work
-    const int pt = ((long long)((a.P + 31) / 32) * a.heads * a.batch >= 2LL * sms) ? 32 : 16;
-    const dim3 grid((a.P + pt - 1) / pt, a.heads, a.batch);
+    const int pt = ((long long)((a.P + 31) / 32) * a.heads * zdim >= 2LL * sms) ? 32 : 16;
+    const dim3 grid((a.P + pt - 1) / pt, a.heads, zdim);
     if (grid.y > 65535 || grid.z > 65535) return tb_refuse("mamba2: too many heads or sequences for one launch");
     const int nv = (a.N + 31) / 32;
     const int es = dtype == TB_BF16 ? 2 : 4;
     const int chn = a.heads * a.P + 2 * a.groups * a.N;
     const bool vec8 = a.N % 8 == 0 && ((size_t)chn * es) % 16 == 0 && ((size_t)a.heads * a.P * es) % 16 == 0 &&
                       ((uintptr_t)a.xbc & 15) == 0;
-#define SCAN2(NV_, PT_) do { \
+#define SCAN4(NV_, PT_, V8_, MODE_) \
+        DISPATCH2(dtype, w_dtype, tb_launch(mamba2_scan_kernel<T, TW, NV_, PT_, V8_, MODE_>, dim3(grid), dim3(SCAN_NS * (PT_) / SCAN_PP), smem, stream, a))
+#define SCAN3(NV_, PT_, MODE_) do { \
         const size_t smem = (size_t)(SCAN_TT * 2 * (NV_) * 32 + SCAN_TT * (PT_) + SCAN_TT * 2) * sizeof(float); \
-        if (vec8) DISPATCH2(dtype, w_dtype, tb_launch(mamba2_scan_kernel<T, TW, NV_, PT_, true>, dim3(grid), dim3(SCAN_NS * (PT_) / SCAN_PP), smem, stream, a)); \
-        else DISPATCH2(dtype, w_dtype, tb_launch(mamba2_scan_kernel<T, TW, NV_, PT_, false>, dim3(grid), dim3(SCAN_NS * (PT_) / SCAN_PP), smem, stream, a)); \
+        if (vec8) SCAN4(NV_, PT_, true, MODE_); else SCAN4(NV_, PT_, false, MODE_); \
     } while (0)
-#define SCAN(NV_) do { if (pt == 32) SCAN2(NV_, 32); else SCAN2(NV_, 16); } while (0)
-    if (nv <= 1) SCAN(1); else if (nv <= 2) SCAN(2); else if (nv <= 4) SCAN(4); else SCAN(8);
+#define SCAN2(NV_, MODE_) do { if (pt == 32) SCAN3(NV_, 32, MODE_); else SCAN3(NV_, 16, MODE_); } while (0)
+#define SCAN(MODE_) do { if (nv <= 1) SCAN2(1, MODE_); else if (nv <= 2) SCAN2(2, MODE_); else if (nv <= 4) SCAN2(4, MODE_); else SCAN2(8, MODE_); } while (0)
+    if (!chunked) {
+        SCAN(0);
+        return tb_launch_status();
+    }
+    SCAN(1);
+    const int st = tb_launch_status();
+    if (st) return st;
+    SCAN(2);
 #undef SCAN
 #undef SCAN2
+#undef SCAN3
+#undef SCAN4
     return tb_launch_status();
 }
 

@@ -420,7 +420,8 @@ class _Mamba2Args(ctypes.Structure):
                 ("norm_w", c_void_p), ("eps", c_float),
                 ("state", c_void_p), ("state_stride", c_longlong),
                 ("seq_start", c_void_p), ("token_seq", c_void_p), ("slot_ids", c_void_p),
-                ("xbc", c_void_p), ("y", c_void_p), ("out", c_void_p), ("batch", c_int), ("n_tokens", c_int)]
+                ("xbc", c_void_p), ("y", c_void_p), ("out", c_void_p), ("batch", c_int), ("n_tokens", c_int),
+                ("chunk_state", c_void_p), ("chunk_decay", c_void_p), ("chunk_len", c_int), ("n_chunks", c_int)]
 
 
 def mamba2_state_size(heads: int, P: int, N: int, groups: int, taps: int) -> int:
@@ -431,10 +432,12 @@ def mamba2_state_size(heads: int, P: int, N: int, groups: int, taps: int) -> int
 def mamba2(proj: torch.Tensor, dt_raw: torch.Tensor, heads: int, P: int, N: int, groups: int, taps: int, norm_groups: int,
            conv_w: torch.Tensor, conv_b: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor,
            norm_w: torch.Tensor, eps: float, state: torch.Tensor, seq_start: torch.Tensor, token_seq: torch.Tensor,
-           slot_ids: torch.Tensor, batch: int, one_token_each: bool) -> torch.Tensor:
+           slot_ids: torch.Tensor, batch: int, one_token_each: bool, max_seq_len: int = 0) -> torch.Tensor:
     """Everything of the state-space mixer between its two products (see mamba2.cu): from the input product's rows
     ``proj`` [T, inner + channels] (compute dtype) and step sizes ``dt_raw`` [T, heads] (float32, before bias and
-    softplus) to the gated, normed [T, inner] that the output product reads, with the sequences' states (``state`` [slots, mamba2_state_size] float32, rows picked by ``slot_ids``) carried along."""
+    softplus) to the gated, normed [T, inner] that the output product reads, with the sequences' states (``state`` [slots, mamba2_state_size] float32, rows picked by ``slot_ids``) carried along.
+    ``max_seq_len`` (the longest sequence of a step of whole prompts, 0 if unknown) lets few long prompts be cut into
+    chunks that run side by side."""
     _cuda(proj, dt_raw, conv_w, conv_b, dt_bias, A_log, D, norm_w, state, seq_start, token_seq, slot_ids)
     inner, ch = heads * P, heads * P + 2 * groups * N
     _rows_contig(proj, "mamba2: proj")
@@ -465,10 +468,20 @@ def mamba2(proj: torch.Tensor, dt_raw: torch.Tensor, heads: int, P: int, N: int,
     a.seq_start = seq_start.data_ptr(); a.token_seq = token_seq.data_ptr(); a.slot_ids = slot_ids.data_ptr()
     a.xbc = xbc.data_ptr(); a.y = y.data_ptr(); a.out = out.data_ptr(); a.batch = batch; a.n_tokens = T
     lib = build.load("mamba2")
+    scan_launches = 1
+    if not one_token_each and max_seq_len > 0:
+        chunk_len = c_int(0)
+        n_chunks = int(lib.tb_mamba2_plan(c_int(heads), c_int(P), c_int(batch), c_int(int(max_seq_len)), ctypes.byref(chunk_len)))
+        if n_chunks > 1:
+            chunk_state = torch.empty((batch, n_chunks, heads * P * N), dtype=torch.float32, device=proj.device)
+            chunk_decay = torch.empty((batch, n_chunks, heads), dtype=torch.float32, device=proj.device)
+            a.chunk_state = chunk_state.data_ptr(); a.chunk_decay = chunk_decay.data_ptr()
+            a.chunk_len = chunk_len.value; a.n_chunks = n_chunks
+            scan_launches = 2
     cd, cw = c_int(code(dt)), c_int(code(wd))
     _check(lib, lib.tb_mamba2_conv(ctypes.byref(a), cd, cw, c_int(int(bool(one_token_each))), _stream()), "mamba2_conv",
            1 if one_token_each or taps == 1 else 2)
-    _check(lib, lib.tb_mamba2_scan(ctypes.byref(a), cd, cw, _stream()), "mamba2_scan")
+    _check(lib, lib.tb_mamba2_scan(ctypes.byref(a), cd, cw, _stream()), "mamba2_scan", scan_launches)
     _check(lib, lib.tb_mamba2_gate_norm(ctypes.byref(a), cd, cw, _stream()), "mamba2_gate_norm")
     return out
 

@@ -89,7 +89,8 @@ class Mamba2(Mixer):
         w = self.w
         y = ops.mamba2(proj, dt_raw, self.heads, self.P, self.N, self.groups, self.taps, self.norm_groups, w["conv_w"],
                        w["conv_b"], w["dt_bias"], w["A_log"], w["D"], w["norm"], self.eps, state.data, ctx.seq_start,
-                       ctx.token_seq, ctx.slot_ids, ctx.batch, one_token_each=not ctx.is_prefill)
+                       ctx.token_seq, ctx.slot_ids, ctx.batch, one_token_each=not ctx.is_prefill,
+                       max_seq_len=ctx.max_seq_len if ctx.is_prefill else 0)
         return linear_partials(y, self.w_o)
 
 
