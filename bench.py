@@ -213,10 +213,12 @@ def design_kernels(torch, size, hbm_gbs, tokens=PREFILL_TOKENS):
     T = tokens
     out = {}
 
-    def rec(name, us, nbytes, flops=0.0, like=None):
+    def rec(name, us, nbytes, flops=0.0, like=None, tensor_flops=0.0):
         t_mem, t_fl = nbytes / (hbm_gbs * 1e9) * 1e6, flops / (FP32_TFLOPS_NOMINAL * 1e12) * 1e6
-        out[name] = {"us": round(us, 1), "bytes": int(nbytes), "roofline_us": round(max(t_mem, t_fl), 1),
-                     "frac": round(max(t_mem, t_fl) / us, 3), "bound": "fp32" if t_fl > t_mem else "hbm"}
+        t_tc = tensor_flops / (peaks()[1] * 1e12) * 1e6
+        best = max(t_mem, t_fl, t_tc)
+        out[name] = {"us": round(us, 1), "bytes": int(nbytes), "roofline_us": round(best, 1), "frac": round(best / us, 3),
+                     "bound": "tensor" if best == t_tc else ("fp32" if best == t_fl else "hbm")}
         if like:
             out[name]["like"] = like
     pos = torch.arange(T, device=dev).int()
@@ -249,8 +251,25 @@ def design_kernels(torch, size, hbm_gbs, tokens=PREFILL_TOKENS):
     # conv + recurrence + gated norm together (three launches, four with the state's update): bytes of the rows
     # they read and write once, FLOPs of the recurrence (5 per state element and token, 32-bit)
     rec("mamba2 (conv, scan, gated norm)",
-        _median_us(torch, lambda: ops.mamba2(proj, dtr, mh, mp, N, 1, 4, 1, cw, cb, dtb, Al, D, nw, 1e-5, state, ss, tseq, slots, 1, False), flush),
+        _median_us(torch, lambda: ops.mamba2(proj, dtr, mh, mp, N, 1, 4, 1, cw, cb, dtb, Al, D, nw, 1e-5, state, ss, tseq, slots, 1, False,
+                                             max_seq_len=T), flush),
         T * (ch * 2 * 3 + inner * 2 + inner * 4 * 2 + inner * 2), flops=T * inner * N * 5.0, like="attention (prefill)")
+    # the mixer kernel of the closest model (and of this design's attention layers): causal attention of the prompt
+    q = torch.randn(T, (H + 2 * G) * d, device=dev).to(bf)
+    rec("attention (prefill)",
+        _median_us(torch, lambda: ops.attn_prefill(q[:, :H * d], q[:, H * d:(H + G) * d], q[:, (H + G) * d:], ss, tseq, H, G, d,
+                                                   d ** -0.5, 30.0, 0, T, [T], {}), flush),
+        T * (H + 2 * G) * d * 2 + T * H * d * 2, tensor_flops=4.0 * H * d * T * (T + 1) / 2)
+    # one token for each of 64 sequences: the state is read and written once
+    B = 64
+    proj1 = torch.randn(B, inner + ch, device=dev).to(bf)
+    dtr1 = torch.randn(B, mh, device=dev)
+    state64 = torch.zeros(B, ops.mamba2_state_size(mh, mp, N, 1, 4), device=dev)
+    ss1 = torch.arange(B + 1, device=dev).int()
+    tseq1 = torch.arange(B, device=dev).int()
+    rec("mamba2, one token for each of 64 sequences",
+        _median_us(torch, lambda: ops.mamba2(proj1, dtr1, mh, mp, N, 1, 4, 1, cw, cb, dtb, Al, D, nw, 1e-5, state64, ss1, tseq1, tseq1, B, True), flush),
+        state64.numel() * 8, like="attention (decode)")
     return out
 
 
