@@ -149,12 +149,12 @@ FP32_TFLOPS_NOMINAL = 72.0      # 148 SMs x 128 FMA x 2 x 1.9 GHz: the bound of 
 
 def divanex_config(size):
     W, L, H, G, d, ff, mh, mp, N, V = DESIGN_SIZES[size]
-    attn = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "softcap": 30.0,
-                                           "q_temp": {"coef": 0.5, "every": 64}},
+    attn = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "softcap": 50.0,
+                                           "q_temp": {"coef": 0.3, "every": 128}},
             "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}}
     ssm = {"type": "mamba2", "mixer": {"heads": mh, "vdim": mp, "state": N, "groups": 1, "conv": 4, "norm_groups": 1}, "mlp": None}
-    return {"architecture": "Divanex", "vocab": V, "width": W, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
-            "postln_alpha": 2.0, "logit_scale": 0.25, "token_side": {"dim": 64},
+    return {"architecture": "Divanex", "vocab": V, "width": W, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "postln_alpha": 1.5, "logit_scale": 0.5, "token_side": {"dim": 64},
             "layers": [attn if i % 2 == 0 else ssm for i in range(L)]}
 
 

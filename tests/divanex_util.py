@@ -52,11 +52,11 @@ CFG_B = config(301, 72, [
 # C: sizes that the tensor-core kernels take in bfloat16 (head size 64, a state of 64, widths that are multiples
 #    of 64), four query heads per kv head.
 CFG_C = config(512, 128, [
-    ("attention", attn(4, 1, 64, 0.5, softcap=30.0, q_temp=(0.5, 32)), dense(256, 1.5)),
+    ("attention", attn(4, 1, 64, 0.5, softcap=25.0, q_temp=(0.4, 32)), dense(256, 1.5)),
     ("mamba2", ssm(4, 32, 64, 2, 4, 1), None),
     ("attention", attn(2, 2, 64, 0.4), None),
     ("mamba2", ssm(2, 64, 32, 1, 4, 2), dense(128, 1.0)),
-], alpha=2.0, logit_scale=0.25, emb_scale=8.0, eps=1e-6, side=16)
+], alpha=1.75, logit_scale=0.125, emb_scale=8.0, eps=1e-6, side=32)
 
 CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C}
 

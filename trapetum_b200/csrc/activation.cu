@@ -75,9 +75,11 @@ extern "C" int tb_gated_act_limit(const void* gu, int in_dtype, void* out, int o
 }
 
 // out[t, j] = gelu_tanh(g[t, j]) * table[ids[t], col0 + j]: the gate of a side input that is looked up by token id.
+// g may come as n_splits partial sums (the split-K output of its product), added here in split order.
 template <typename TI, typename TW, typename TO>
-__global__ void token_gate_kernel(const TI* __restrict__ g, const int* __restrict__ ids, const TW* __restrict__ table,
-                                  long long table_stride, int col0, int vocab, TO* __restrict__ out, int dim) {
+__global__ void token_gate_kernel(const TI* __restrict__ g, int n_splits, long long split_stride, const int* __restrict__ ids,
+                                  const TW* __restrict__ table, long long table_stride, int col0, int vocab,
+                                  TO* __restrict__ out, int dim) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t t = blockIdx.x;
@@ -85,16 +87,19 @@ __global__ void token_gate_kernel(const TI* __restrict__ g, const int* __restric
     if (j >= dim) return;
     const int id = ids[t];
     const float e = (id >= 0 && id < vocab) ? to_f<TW>(table[(size_t)id * table_stride + col0 + j]) : __int_as_float(0x7fc00000);
-    out[t * dim + j] = from_f<TO>(gelu_tanh_f(to_f<TI>(g[t * dim + j])) * e);
+    float v = to_f<TI>(g[t * dim + j]);
+    for (int s = 1; s < n_splits; s++) v += to_f<TI>(g[(size_t)s * split_stride + t * dim + j]);
+    out[t * dim + j] = from_f<TO>(gelu_tanh_f(v) * e);
 }
 
-extern "C" int tb_token_gate(const void* g, int g_dtype, const int* ids, const void* table, int table_dtype,
+extern "C" int tb_token_gate(const void* g, int g_dtype, int n_splits, long long split_stride, const int* ids, const void* table, int table_dtype,
                              long long table_stride, int col0, int vocab, void* out, int out_dtype, int rows, int dim,
                              cudaStream_t stream) {
     if (rows <= 0 || dim <= 0) return 0;
     dim3 grid(rows, (dim + 127) / 128);
     if (grid.y > 65535) return tb_refuse("token_gate: dim %d is too wide", dim);
-#define LAUNCH(TI, TW, TO) tb_launch(token_gate_kernel<TI, TW, TO>, dim3(grid), dim3(128), 0, stream, (const TI*)g, ids, \
+    if (n_splits < 1) return tb_refuse("token_gate: n_splits=%d", n_splits);
+#define LAUNCH(TI, TW, TO) tb_launch(token_gate_kernel<TI, TW, TO>, dim3(grid), dim3(128), 0, stream, (const TI*)g, n_splits, split_stride, ids, \
                                      (const TW*)table, table_stride, col0, vocab, (TO*)out, dim)
 #define LAUNCH_O(TI, TW) do { if (out_dtype == TB_F32) LAUNCH(TI, TW, float); else LAUNCH(TI, TW, bf16); } while (0)
     if (out_dtype != TB_F32 && out_dtype != TB_BF16) return tb_refuse("token_gate: unknown output dtype %d", out_dtype);

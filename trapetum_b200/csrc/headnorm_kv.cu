@@ -40,24 +40,25 @@ template <> __device__ __forceinline__ void store4<bf16>(bf16* p, const float* f
 
 // VEC = 4: head_dim and all row strides are multiples of 4 and the bases 16-byte aligned; a lane then holds groups of
 // four neighbouring elements (one 16-byte load per split, one 8- or 16-byte store per destination).
-#define HN_AT_ONCE 4              // head slots a warp works on at a time: their loads are requested together
+// AT_ONCE: head slots a warp works on at a time (their loads are requested together): four for many tokens, one for
+// few, where a warp's chain of dependent loads (position, page, rows) is the launch's whole time.
 
 // GROUPS: groups of VEC elements a lane holds of one head (head_dim <= 32 * VEC * GROUPS).
-template <typename T, int VEC, int GROUPS>
+template <typename T, int VEC, int GROUPS, int AT_ONCE>
 __global__ void __launch_bounds__(256) headnorm_kv_kernel(HeadNormKvArgs a, int n_tokens) {
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int in_slots = a.n_heads + a.n_kv_heads * (a.v_from_k ? 1 : 2);
     const int n_items = n_tokens * in_slots;                         // (the host refuses what does not fit 31 bits)
-    const int item0 = (blockIdx.x * (blockDim.x >> 5) + warp) * HN_AT_ONCE;
+    const int item0 = (blockIdx.x * (blockDim.x >> 5) + warp) * AT_ONCE;
     if (item0 >= n_items) return;
     const int hd = a.head_dim;
     constexpr int groups = GROUPS;
 
-    float x[HN_AT_ONCE][GROUPS][VEC];
+    float x[AT_ONCE][GROUPS][VEC];
 #pragma unroll
-    for (int u = 0; u < HN_AT_ONCE; u++) {
+    for (int u = 0; u < AT_ONCE; u++) {
         const int item = item0 + u;
         const int t = item / in_slots, hs = item - t * in_slots;
         const float* src = a.partial + (size_t)t * a.partial_row_stride + (size_t)hs * hd;
@@ -80,7 +81,7 @@ __global__ void __launch_bounds__(256) headnorm_kv_kernel(HeadNormKvArgs a, int 
         }
     }
 #pragma unroll
-    for (int u = 0; u < HN_AT_ONCE; u++) {
+    for (int u = 0; u < AT_ONCE; u++) {
         const int item = item0 + u;
         if (item >= n_items) break;                                  // (the same in every lane)
         const int t = item / in_slots, hs = item - t * in_slots;
@@ -156,12 +157,16 @@ extern "C" int tb_headnorm_kv(const HeadNormKvArgs* args, int out_dtype, int n_t
         return tb_refuse("headnorm_kv: ring_rows=%d must be a multiple of page_rows=%d", a.ring_rows, a.page_rows);
     const int in_slots = a.n_heads + a.n_kv_heads * (a.v_from_k ? 1 : 2);
     const long long items = (long long)n_tokens * in_slots;
-    const long long blocks = (items + 8 * HN_AT_ONCE - 1) / (8 * HN_AT_ONCE);
-    if (items + 8 * HN_AT_ONCE > 0x7fffffffLL) return tb_refuse("headnorm_kv: too many tokens");
+    const int at_once = items >= 8192 ? 4 : 1;
+    const long long blocks = (items + 8 * at_once - 1) / (8 * at_once);
+    if (items + 32 > 0x7fffffffLL) return tb_refuse("headnorm_kv: too many tokens");
     auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
     const bool vec = a.head_dim % 4 == 0 && a.split_stride % 4 == 0 && a.partial_row_stride % 4 == 0 &&
                      a.out_row_stride % 4 == 0 && al16(a.partial) && al16(a.out) && al16(a.k_pool) && al16(a.v_pool);
-#define HN(VEC_, G_) TB_DISPATCH_1(out_dtype, T, tb_launch(headnorm_kv_kernel<T, VEC_, G_>, dim3((unsigned)blocks), dim3(256), 0, stream, a, n_tokens))
+#define HN(VEC_, G_) do { \
+        if (at_once == 4) TB_DISPATCH_1(out_dtype, T, tb_launch(headnorm_kv_kernel<T, VEC_, G_, 4>, dim3((unsigned)blocks), dim3(256), 0, stream, a, n_tokens)); \
+        else TB_DISPATCH_1(out_dtype, T, tb_launch(headnorm_kv_kernel<T, VEC_, G_, 1>, dim3((unsigned)blocks), dim3(256), 0, stream, a, n_tokens)); \
+    } while (0)
     if (vec) { if (a.head_dim <= 128) HN(4, 1); else if (a.head_dim <= 256) HN(4, 2); else HN(4, 4); }
     else { if (a.head_dim <= 128) HN(1, 4); else HN(1, 16); }
 #undef HN

@@ -30,7 +30,8 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 
 struct Mamba2Args {
     const void* proj; long long proj_stride;      // [tokens][inner + channels], compute dtype
-    const float* dt; long long dt_stride;          // [tokens][heads], the step sizes before bias and softplus
+    const float* dt; long long dt_stride;          // [tokens][heads], the step sizes before bias and softplus,
+    int dt_splits; long long dt_split_stride;      // as dt_splits partial sums (added in split order)
     int heads, P, N, groups, taps, norm_groups;
     const void* conv_w; const void* conv_b;        // [channels][taps], [channels]   (weights' dtype)
     const void* dt_bias; const void* A_log; const void* D;   // [heads]
@@ -245,7 +246,11 @@ __global__ void __launch_bounds__(SCAN_NS * PT / SCAN_PP) mamba2_scan_kernel(Mam
             const int tt = i / PT, pp = p0 + i % PT;
             pre_x[l] = (tt < nt && pp < P) ? to_f<T>(xbc[(size_t)(tb + tt) * ch + h * P + pp]) : 0.f;
         }
-        if (threadIdx.x < nt) pre_dt = a.dt[(size_t)(tb + threadIdx.x) * a.dt_stride + h];
+        if (threadIdx.x < nt) {
+            const float* q = a.dt + (size_t)(tb + threadIdx.x) * a.dt_stride + h;
+            pre_dt = q[0];
+            for (int sp = 1; sp < a.dt_splits; sp++) pre_dt += q[(size_t)sp * a.dt_split_stride];
+        }
     };
     auto commit = [&](int tb) {                                      // registers (or, without VEC8, memory) to shared memory
         const int nt = min(SCAN_TT, s1 - tb);
@@ -359,6 +364,50 @@ __global__ void mamba2_gate_norm_kernel(Mamba2Args a) {
     for (int i = threadIdx.x; i < gs; i += blockDim.x) {
         const float v = y[i] * silu_f(to_f<T>(z[i]));
         out[i] = from_f<T>(v * r * to_f<TW>(w[i]));
+    }
+}
+
+// The same for few tokens, where the launch's time is its chain of memory round trips: a thread keeps its NV groups
+// of four columns in registers, so y and z are read once (group sizes up to 1,024 x 4 x NV that are multiples of 4).
+template <typename T, typename TW, int NV>
+__global__ void __launch_bounds__(1024) mamba2_gate_norm_few_kernel(Mamba2Args a) {
+    pdl_launch_dependents();
+    __shared__ float red[33];
+    const int inner = a.heads * a.P, gs = inner / a.norm_groups;
+    const int t = blockIdx.x, c0 = blockIdx.y * gs;
+    float w[NV][4], v[NV][4];
+#pragma unroll
+    for (int k = 0; k < NV; k++) {
+        const int i = (threadIdx.x + k * blockDim.x) * 4;
+#pragma unroll
+        for (int e = 0; e < 4; e++) w[k][e] = i < gs ? to_f<TW>(((const TW*)a.norm_w)[c0 + i + e]) : 0.f;
+    }
+    pdl_wait();
+    const float* y = a.y + (size_t)t * inner + c0;
+    const T* z = (const T*)a.proj + (size_t)t * a.proj_stride + c0;
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; k++) {
+        const int i = (threadIdx.x + k * blockDim.x) * 4;
+#pragma unroll
+        for (int e = 0; e < 4; e++) v[k][e] = 0.f;
+        if (i < gs) {
+            const float4 yy = *(const float4*)(y + i);
+            const float ye[4] = {yy.x, yy.y, yy.z, yy.w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) { v[k][e] = ye[e] * silu_f(to_f<T>(z[i + e])); ss += v[k][e] * v[k][e]; }
+        }
+    }
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)gs + a.eps);
+    T* out = (T*)a.out + (size_t)t * inner + c0;
+#pragma unroll
+    for (int k = 0; k < NV; k++) {
+        const int i = (threadIdx.x + k * blockDim.x) * 4;
+        if (i < gs) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) out[i + e] = from_f<T>(v[k][e] * r * w[k][e]);
+        }
     }
 }
 
@@ -481,6 +530,16 @@ extern "C" int tb_mamba2_gate_norm(const Mamba2Args* args, int dtype, int w_dtyp
     int threads = (gs + 31) / 32 * 32;
     threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
     if (a.norm_groups > 65535) return tb_refuse("mamba2: too many norm groups");
+    if (a.n_tokens <= 64 && gs % 4 == 0 && gs <= 1024 * 4 * 4 && (a.heads * a.P) % 4 == 0 && ((uintptr_t)a.y & 15) == 0) {
+        const int groups4 = gs / 4;
+        const int nvv = groups4 <= 1024 ? 1 : groups4 <= 2048 ? 2 : 4;
+        int th = ((groups4 + nvv - 1) / nvv + 31) / 32 * 32;
+        if (th < 64) th = 64;
+#define FEW(NV_) DISPATCH2(dtype, w_dtype, tb_launch(mamba2_gate_norm_few_kernel<T, TW, NV_>, dim3(a.n_tokens, a.norm_groups), dim3(th), 0, stream, a))
+        if (nvv == 1) FEW(1); else if (nvv == 2) FEW(2); else FEW(4);
+#undef FEW
+        return tb_launch_status();
+    }
     DISPATCH2(dtype, w_dtype, tb_launch(mamba2_gate_norm_kernel<T, TW>, dim3(a.n_tokens, a.norm_groups), dim3(threads), 0, stream, a));
     return tb_launch_status();
 }

@@ -248,8 +248,14 @@ def gated_act(gu: torch.Tensor, activation: str, out_dtype: torch.dtype, limit: 
 def token_gate(g: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, col0: int,
                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """out[t, j] = gelu_tanh(g[t, j]) * table[ids[t], col0 + j], computed in 32-bit, stored in ``out_dtype``
-    (default: g's dtype)."""
+    (default: g's dtype).  ``g``: [tokens, dim], or [splits, tokens, dim] partial sums that are added on the way."""
     _cuda(g, ids, table)
+    n_splits, split_stride = 1, 0
+    if g.dim() == 3:
+        n_splits, split_stride = g.shape[0], g.stride(0)
+        if not g[0].is_contiguous():
+            raise KernelError("token_gate: partial sums must be [splits, tokens, dim] with contiguous [tokens, dim]")
+        g3, g = g, g[0]
     if g.dim() != 2 or not g.is_contiguous():
         raise KernelError("token_gate: g must be contiguous [tokens, dim]")
     if ids.dtype != torch.int32 or ids.numel() != g.shape[0] or not ids.is_contiguous():
@@ -258,7 +264,7 @@ def token_gate(g: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, col0: in
         raise KernelError(f"token_gate: columns {col0}..{col0 + g.shape[1]} do not lie in a table of shape {tuple(table.shape)}")
     out = torch.empty(g.shape, dtype=out_dtype or g.dtype, device=g.device)
     lib = build.load("activation")
-    _check(lib, lib.tb_token_gate(_ptr(g), c_int(code(g.dtype)), _ptr(ids), _ptr(table), c_int(code(table.dtype)),
+    _check(lib, lib.tb_token_gate(_ptr(g), c_int(code(g.dtype)), c_int(n_splits), c_longlong(split_stride), _ptr(ids), _ptr(table), c_int(code(table.dtype)),
                                   c_longlong(table.stride(0)), c_int(col0), c_int(table.shape[0]), _ptr(out),
                                   c_int(code(out.dtype)), c_int(g.shape[0]), c_int(g.shape[1]), _stream()), "token_gate")
     return out
@@ -415,6 +421,7 @@ def headnorm_kv(partial: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: 
 
 class _Mamba2Args(ctypes.Structure):
     _fields_ = [("proj", c_void_p), ("proj_stride", c_longlong), ("dt", c_void_p), ("dt_stride", c_longlong),
+                ("dt_splits", c_int), ("dt_split_stride", c_longlong),
                 ("heads", c_int), ("P", c_int), ("N", c_int), ("groups", c_int), ("taps", c_int), ("norm_groups", c_int),
                 ("conv_w", c_void_p), ("conv_b", c_void_p), ("dt_bias", c_void_p), ("A_log", c_void_p), ("D", c_void_p),
                 ("norm_w", c_void_p), ("eps", c_float),
@@ -435,7 +442,7 @@ def mamba2(proj: torch.Tensor, dt_raw: torch.Tensor, heads: int, P: int, N: int,
            slot_ids: torch.Tensor, batch: int, one_token_each: bool, max_seq_len: int = 0) -> torch.Tensor:
     """Everything of the state-space mixer between its two products (see mamba2.cu): from the input product's rows
     ``proj`` [T, inner + channels] (compute dtype) and step sizes ``dt_raw`` [T, heads] (float32, before bias and
-    softplus) to the gated, normed [T, inner] that the output product reads, with the sequences' states (``state`` [slots, mamba2_state_size] float32, rows picked by ``slot_ids``) carried along.
+    softplus; or [splits, T, heads] partial sums) to the gated, normed [T, inner] that the output product reads, with the sequences' states (``state`` [slots, mamba2_state_size] float32, rows picked by ``slot_ids``) carried along.
     ``max_seq_len`` (the longest sequence of a step of whole prompts, 0 if unknown) lets few long prompts be cut into
     chunks that run side by side."""
     _cuda(proj, dt_raw, conv_w, conv_b, dt_bias, A_log, D, norm_w, state, seq_start, token_seq, slot_ids)
@@ -444,8 +451,10 @@ def mamba2(proj: torch.Tensor, dt_raw: torch.Tensor, heads: int, P: int, N: int,
     T = proj.shape[0]
     if proj.shape[1] != inner + ch:
         raise KernelError(f"mamba2: the input product has {proj.shape[1]} columns, the sizes ask for {inner + ch}")
-    if dt_raw.dtype != torch.float32 or tuple(dt_raw.shape) != (T, heads) or dt_raw.stride(1) != 1:
-        raise KernelError(f"mamba2: the step sizes must be float32 [{T}, {heads}], got {tuple(dt_raw.shape)} {dt_raw.dtype}")
+    if dt_raw.dim() == 2:
+        dt_raw = dt_raw[None]
+    if dt_raw.dtype != torch.float32 or tuple(dt_raw.shape[1:]) != (T, heads) or dt_raw.stride(2) != 1:
+        raise KernelError(f"mamba2: the step sizes must be float32 [splits, {T}, {heads}], got {tuple(dt_raw.shape)} {dt_raw.dtype}")
     wd = conv_w.dtype
     for name, t, shape in (("conv", conv_w, (ch, taps)), ("conv bias", conv_b, (ch,)), ("dt_bias", dt_bias, (heads,)),
                            ("A_log", A_log, (heads,)), ("D", D, (heads,)), ("norm", norm_w, (inner,))):
@@ -460,7 +469,8 @@ def mamba2(proj: torch.Tensor, dt_raw: torch.Tensor, heads: int, P: int, N: int,
     out = torch.empty((T, inner), dtype=dt, device=proj.device)
     a = _Mamba2Args()
     a.proj = proj.data_ptr(); a.proj_stride = proj.stride(0)
-    a.dt = dt_raw.data_ptr(); a.dt_stride = dt_raw.stride(0)
+    a.dt = dt_raw.data_ptr(); a.dt_stride = dt_raw.stride(1)
+    a.dt_splits = dt_raw.shape[0]; a.dt_split_stride = dt_raw.stride(0)
     a.heads = heads; a.P = P; a.N = N; a.groups = groups; a.taps = taps; a.norm_groups = norm_groups
     a.conv_w = conv_w.data_ptr(); a.conv_b = conv_b.data_ptr(); a.dt_bias = dt_bias.data_ptr()
     a.A_log = A_log.data_ptr(); a.D = D.data_ptr(); a.norm_w = norm_w.data_ptr(); a.eps = eps

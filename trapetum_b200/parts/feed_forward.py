@@ -120,7 +120,7 @@ class TokenGated(FeedForward):
     def forward(self, x, ctx):
         if ctx.token_ids is None:
             raise RuntimeError("token_gated: the step's context carries no token ids")
-        g = linear(x, self.w_gate, torch.float32)          # narrow: kept 32-bit up to the activation
+        g = linear_partials(x, self.w_gate)                # narrow: 32-bit (partial sums) up to the activation
         return linear_partials(ops.token_gate(g, ctx.token_ids, self.table, self.first_col, self.rt.dtype), self.w_proj)
 
 

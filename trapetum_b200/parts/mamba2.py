@@ -85,7 +85,7 @@ class Mamba2(Mixer):
 
     def forward(self, x, ctx, state):
         proj = linear(x, self.w_in, self.rt.dtype)
-        dt_raw = linear(x, self.w_dt, torch.float32)
+        dt_raw = linear_partials(x, self.w_dt)              # [splits, T, heads], added up by the recurrence's kernel
         w = self.w
         y = ops.mamba2(proj, dt_raw, self.heads, self.P, self.N, self.groups, self.taps, self.norm_groups, w["conv_w"],
                        w["conv_b"], w["dt_bias"], w["A_log"], w["D"], w["norm"], self.eps, state.data, ctx.seq_start,
