@@ -228,6 +228,24 @@ def test_whole_prompts_and_every_layer(folders, oracles, name, dtype):
     eng.check_kernels()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_then_decoding(folders, oracles, dtype):
+    """A prompt of twenty pages: the recurrence runs as chunks side by side, attention over many pages; then tokens one
+    by one on top of it."""
+    name = "A"
+    cfg, w = oracles[name]
+    (ids,) = prompts(cfg["vocab"], [1300 + 6], seed=77)
+    truth = plain.forward(cfg, w, ids)
+    eng = tb.Engine(model_of(folders, name, dtype), 64 * 22, max_slots=2)
+    s = eng.start(1)
+    places = [0, 1, 63, 64, 500, 1023, 1024, 1298, 1299]
+    got = [eng.step(s, [ids[:1300]], [places])] + [eng.step(s, [[t]], [[0]]).clone() for t in ids[1300:]]
+    eng.release(s)
+    eng.check_kernels()
+    idx = places + list(range(1300, 1306))
+    close(torch.cat(got), truth[idx], tolerance(name, cfg, w, ids, dtype)[idx], "A prompt of 1,300 then one by one", dtype)
+
+
 @pytest.mark.parametrize("name", sorted(CONFIGS))
 def test_the_residual_stream_after_every_layer(folders, oracles, name):
     """Layer by layer in 32-bit: the engine's own blocks on the engine's own stream."""
@@ -262,7 +280,8 @@ def test_the_residual_stream_after_every_layer(folders, oracles, name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name, first", [("A", 1), ("A", 2), ("B", 3), ("B", 63), ("C", 64), ("C", 65), ("A", 130)])
+@pytest.mark.parametrize("name, first", [("A", 1), ("A", 2), ("B", 3), ("B", 63), ("C", 64), ("C", 65), ("A", 130),
+                                         ("D", 5), ("E", 2), ("E", 66)])
 def test_prompt_then_token_by_token(folders, oracles, name, first, dtype):
     """Decoding through the cache and the state, over page borders and over the temperature's steps, long enough
     that the step runs as a captured graph and that the length bucket changes (at 256)."""
