@@ -88,7 +88,13 @@ __global__ void token_gate_kernel(const TI* __restrict__ g, int n_splits, long l
     const int id = ids[t];
     const float e = (id >= 0 && id < vocab) ? to_f<TW>(table[(size_t)id * table_stride + col0 + j]) : __int_as_float(0x7fc00000);
     float v = to_f<TI>(g[t * dim + j]);
-    for (int s = 1; s < n_splits; s++) v += to_f<TI>(g[(size_t)s * split_stride + t * dim + j]);
+    for (int s0 = 1; s0 < n_splits; s0 += 8) {                      // eight splits requested at a time, added in order
+        float p[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) p[k] = s0 + k < n_splits ? to_f<TI>(g[(size_t)(s0 + k) * split_stride + t * dim + j]) : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; k++) if (s0 + k < n_splits) v += p[k];
+    }
     out[t * dim + j] = from_f<TO>(gelu_tanh_f(v) * e);
 }
 
