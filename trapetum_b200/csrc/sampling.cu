@@ -366,13 +366,14 @@ template <int R>
 __device__ void state_before_pass(const SampleWide& w, int row, u64* g, u64* part, SampleState* out) {
     if (threadIdx.x == 0) {
         SampleState st;
-        if (R <= 1) {
-            const float T = w.a.temperature ? w.a.temperature[row] : 0.f;
-            const float tp = w.a.top_p ? w.a.top_p[row] : 1.f;
-            st.mass_above = 0ull; st.want = 0ull; st.prefix = 0u; st.nucleus = (T > 0.f && tp < 1.f) ? 1 : 0;
-        } else {
-            st = w.state[(size_t)row * 3 + (R > 1 ? R - 2 : 0)];
-        }
+        const float T = w.a.temperature ? w.a.temperature[row] : 0.f;
+        const float tp = w.a.top_p ? w.a.top_p[row] : 1.f;
+        const int nucleus = (T > 0.f && tp < 1.f) ? 1 : 0;
+        st.mass_above = 0ull; st.want = 0ull; st.prefix = 0u;
+        // a row without a nucleus leaves no state behind (its CTAs return before they would write it), so whether a
+        // row has one is taken from its own parameters in every pass, never from that memory
+        if (R > 1 && nucleus) st = w.state[(size_t)row * 3 + (R > 1 ? R - 2 : 0)];
+        st.nucleus = nucleus;
         *out = st;
     }
     __syncthreads();
