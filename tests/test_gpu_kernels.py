@@ -590,6 +590,27 @@ def _args(rows, temperature, top_p, penalty, draws):
     return f(temperature), f(top_p), f(penalty), f(draws)
 
 
+def test_wide_sampling_reads_no_scratch_it_did_not_write(ops):
+    """Rows without a nucleus (top_p 1) beside rows with one, on scratch memory that held other bytes before: the
+    draws are those of clean memory."""
+    V, rows = 256000, 8
+    x = rnd(rows, V, s=2.0, seed=3)
+    u = torch.linspace(0.001, 0.999, rows)
+    top_p = torch.tensor([1.0, 0.9, 1.0, 1.0, 0.5, 1.0, 0.95, 1.0])
+    t, p, pen, ud = _args(rows, 1.0, top_p, 1.0, u)
+    torch.cuda.empty_cache()
+    want = ops.sample(x.clone(), t, p, pen, ud, None).cpu()
+    for fill in (0xFF, 0x01, 0x7F):
+        junk = [torch.full((n,), fill, dtype=torch.uint8, device="cuda") for n in (1 << 16, 1 << 18, 1 << 20, 1 << 22, 1 << 24)]
+        del junk                                  # the allocator hands these blocks out again, bytes and all
+        assert torch.equal(ops.sample(x.clone(), t, p, pen, ud, None).cpu(), want)
+    for i in range(rows):
+        probs = plain.nucleus(x[i].cpu(), 1.0, float(top_p[i]))
+        cdf = torch.cumsum(probs, 0)
+        tok = int(want[i])
+        assert probs[tok] > 0 and float(cdf[tok] - probs[tok]) - 1e-4 <= float(u[i]) <= float(cdf[tok]) + 1e-4
+
+
 @pytest.mark.parametrize("V", [1000, 40001])      # one CTA a row; several CTAs a row (the ids lie in different chunks)
 def test_sample_greedy_and_penalty(ops, V):
     a, b, c, d = 10, V - 7, V // 2 + 3, 5

@@ -483,7 +483,8 @@ __global__ void __launch_bounds__(256) sample_pick_kernel(SampleWide w, int nucl
         return;
     }
     unsigned thr = 0u;
-    if (nucleus) { const SampleState st = w.state[(size_t)row * 3 + 2]; if (st.nucleus) thr = st.prefix; }
+    // (only a row with a nucleus has left a state behind: whether it has one is taken from its own parameters)
+    if (nucleus && (a.top_p ? a.top_p[row] : 1.f) < 1.f) thr = w.state[(size_t)row * 3 + 2].prefix;
     for (int c = tid; c < w.n_chunks; c += 256) cm[c] = w.cmass[(size_t)row * w.n_chunks + c];
     const float mx = row_max(w, row, red);                          // (has the barriers that cm needs, too)
     if (tid == 0) {
