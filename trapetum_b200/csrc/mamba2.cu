@@ -423,13 +423,13 @@ static int check(const Mamba2Args& a) {
     return 0;
 }
 
+// The small tensors (taps, biases, A_log, D, the norm's weight) enter 32-bit arithmetic and are taken in 32 bits.
 #define DISPATCH2(ct, cw, ...)                                                             \
     do {                                                                                   \
-        if ((ct) == TB_F32 && (cw) == TB_F32) { typedef float T; typedef float TW; __VA_ARGS__; }        \
-        else if ((ct) == TB_BF16 && (cw) == TB_BF16) { typedef bf16 T; typedef bf16 TW; __VA_ARGS__; }   \
-        else if ((ct) == TB_BF16 && (cw) == TB_F32) { typedef bf16 T; typedef float TW; __VA_ARGS__; }   \
-        else if ((ct) == TB_F32 && (cw) == TB_BF16) { typedef float T; typedef bf16 TW; __VA_ARGS__; }   \
-        else return tb_refuse("mamba2: unknown dtype codes %d %d", (ct), (cw));              \
+        if ((cw) != TB_F32) return tb_refuse("mamba2: the small tensors must be float32 (code %d)", (cw)); \
+        if ((ct) == TB_F32) { typedef float T; typedef float TW; __VA_ARGS__; }            \
+        else if ((ct) == TB_BF16) { typedef bf16 T; typedef float TW; __VA_ARGS__; }       \
+        else return tb_refuse("mamba2: unknown dtype code %d", (ct));                      \
     } while (0)
 
 extern "C" int tb_mamba2_conv(const Mamba2Args* args, int dtype, int w_dtype, int one_token_each, cudaStream_t stream) {

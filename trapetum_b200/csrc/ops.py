@@ -455,7 +455,7 @@ def mamba2(proj: torch.Tensor, dt_raw: torch.Tensor, heads: int, P: int, N: int,
         dt_raw = dt_raw[None]
     if dt_raw.dtype != torch.float32 or tuple(dt_raw.shape[1:]) != (T, heads) or dt_raw.stride(2) != 1:
         raise KernelError(f"mamba2: the step sizes must be float32 [splits, {T}, {heads}], got {tuple(dt_raw.shape)} {dt_raw.dtype}")
-    wd = conv_w.dtype
+    wd = torch.float32          # the small tensors enter 32-bit arithmetic: the kernels take them in 32 bits
     for name, t, shape in (("conv", conv_w, (ch, taps)), ("conv bias", conv_b, (ch,)), ("dt_bias", dt_bias, (heads,)),
                            ("A_log", A_log, (heads,)), ("D", D, (heads,)), ("norm", norm_w, (inner,))):
         if tuple(t.shape) != shape or t.dtype != wd or not t.is_contiguous():
