@@ -103,7 +103,7 @@ def attention_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], pre: str, m: di
     H, G, d = m["heads"], m["kv_heads"], m["dim"]
     q = (h @ w[pre + "q"].T).view(T, H, d)
     kraw = (h @ w[pre + "k"].T).view(T, G, d)
-    v = rnd(kraw)                                            # the values are the keys as projected
+    v = rnd(kraw)                                            # v is the raw k projection (taken before k is normed)
     q = unit_rms(q, eps)
     k = rnd(unit_rms(kraw, eps))
     pos = torch.arange(pos0, pos0 + T)

@@ -104,7 +104,7 @@ class DivanexConfig:
                 dim = _sub(m, "dim", int, mw)
                 vdim = _sub(m, "vdim", int, mw, dim)
                 if vdim != dim:
-                    raise ConfigError(f"config.json: {mw}vdim is {vdim} but the values are the keys, of size {dim}")
+                    raise ConfigError(f"config.json: {mw}vdim is {vdim}, but v is the k projection itself, whose heads have size {dim}")
                 if heads < 1 or kv < 1 or heads % kv:
                     raise ConfigError(f"config.json: {mw}heads={heads} cannot share kv_heads={kv}")
                 qt = _obj(m, "q_temp", mw, nullable=True) or {}

@@ -4,7 +4,7 @@ Nothing here computes.  A Divanex layer is a ``post_norm`` block (the norm after
 by ``postln_alpha`` on the way in) around one of two mixers and an optional dense feed-forward, followed by a
 side input that is looked up by token id:
 
-* ``attention``: no rotation; the values are the keys as projected; q and k heads divided by their root mean
+* ``attention``: no rotation; no v matrix (v is the raw output of the k projection); q and k heads divided by their root mean
   square; a query temperature that grows with the logarithm of the position; scaled, soft-capped scores; causal
   softmax.  All of it is the framework's attention part with the matching parameters.
 * ``mamba2``: the state-space part of :mod:`trapetum_b200.parts.mamba2`.

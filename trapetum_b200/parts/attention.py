@@ -25,7 +25,7 @@ Three more options serve mixers whose positions do not enter through a rotation
 (``position`` of kind "none"); they run in one kernel between the projection and
 the attention kernel (``ops.headnorm_kv``), all in 32-bit:
 
-* ``v`` None: the values are the keys as projected (no v matrix; the cache still
+* ``v`` None: there is no v matrix, v is the raw output of the k projection (the cache still
   keeps keys and values, because the keys may be normed and the values are not);
 * ``head_unit_norm`` ``{"q": bool, "k": bool, "eps": e}``: every query / key head is
   divided by its root mean square over ``head_dim`` (no weight);

@@ -7,7 +7,7 @@ groups * state columns of B and of C, one dt per head) and an output product ``W
   token's) and silu;
 * ``dt = softplus(dt + dt_bias)``; per head, with B and C of its group, the state S [head_dim, state] goes
   ``S <- exp(-exp(A_log) dt) S + dt x B^T`` and the output is ``y = S C + D x``;
-* ``y * silu(z)`` is RMS-normed in ``norm_groups`` equal parts (the gate before the norm), times a weight.
+* ``y * silu(z)`` is RMS-normed in ``norm_groups`` equal parts (gating first, then the norm), times a weight.
 
 A sequence's state (S and the last ``conv - 1`` convolution inputs) is one float32 row of the cache's state
 area, addressed by slot, zero when the sequence starts.  The step sizes (they enter an exponential), softplus,
