@@ -1,0 +1,190 @@
+"""Lofirax, stated plainly: one slow function per mechanism, in 64-bit floats on the CPU.
+
+This file is the tests' oracle.  It shares no code with the library: it reads a
+configuration dictionary (the keys of config.json) and a dictionary of tensors by
+name, and runs one sequence token by token where the mechanism is a recurrence.
+
+Notation: ``W`` is the model's width, ``h`` a mixer's or feed-forward's input
+[tokens, W], all matrices are stored [out, in].
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+F = torch.float64
+
+
+def f64(t: torch.Tensor) -> torch.Tensor:
+    return t.to(F)
+
+
+def layer_norm(x, w, b, eps):
+    mu = x.mean(-1, keepdim=True)
+    var = ((x - mu) ** 2).mean(-1, keepdim=True)
+    return (x - mu) / torch.sqrt(var + eps) * w + b
+
+
+def rms_norm(x, w, eps):
+    return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w
+
+
+def gelu_tanh(z):
+    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
+
+
+def silu(z):
+    return z * torch.sigmoid(z)
+
+
+def gated(h, gate, up, down, act):
+    return (act(h @ gate.T) * (h @ up.T)) @ down.T
+
+
+def gla(h, m: dict, t: Dict[str, torch.Tensor], p: str, eps: float, state: Optional[torch.Tensor] = None):
+    """Gated linear attention over one sequence.  ``state`` [heads, dim, vdim] is carried in and returned."""
+    H, D, V, tau = m["heads"], m["dim"], m["vdim"], float(m["tau"])
+    T = h.shape[0]
+    q = (h @ t[p + "q"].T).view(T, H, D) * D ** -0.5
+    k = (h @ t[p + "k"].T).view(T, H, D)
+    v = (h @ t[p + "v"].T).view(T, H, V)
+    z = (h @ t[p + "a1"].T) @ t[p + "a2"].T + t[p + "a2.b"]
+    alpha = torch.sigmoid(z).pow(1.0 / tau).view(T, H, D)
+    S = torch.zeros(H, D, V, dtype=F) if state is None else state.clone()
+    o = torch.zeros(T, H, V, dtype=F)
+    for i in range(T):
+        S = alpha[i][:, :, None] * S + k[i][:, :, None] * v[i][:, None, :]
+        o[i] = torch.einsum("hdv,hd->hv", S, q[i])
+    o = rms_norm(o, t[p + "norm"], eps).reshape(T, H * V)
+    return (o * silu(h @ t[p + "g"].T)) @ t[p + "o"].T, S
+
+
+def rotate_half(x, pos, dims: int, base: float):
+    """The first ``dims`` entries of the last axis, pair (i, i + dims/2), turned by pos * base^(-2i/dims)."""
+    half = dims // 2
+    f = torch.tensor([base ** (-2.0 * i / dims) for i in range(half)], dtype=F)
+    a = pos.to(F)[:, None] * f
+    shape = [x.shape[0]] + [1] * (x.dim() - 2) + [half]
+    c, s = torch.cos(a).view(shape), torch.sin(a).view(shape)
+    u, w = x[..., :half], x[..., half:dims]
+    return torch.cat([u * c - w * s, w * c + u * s, x[..., dims:]], dim=-1)
+
+
+def latent_attention(h, m: dict, t: Dict[str, torch.Tensor], p: str, eps: float, first_pos: int = 0, past=None):
+    """Latent attention over one sequence.  ``past`` = (latents, rotated key parts) of earlier tokens."""
+    H, D, R, V, C = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    T = h.shape[0]
+    pos = torch.arange(first_pos, first_pos + T)
+    q = (h @ t[p + "q"].T).view(T, H, D + R)
+    q_plain, q_rot = q[..., :D], rotate_half(q[..., D:], pos, m["rot"]["dims"], float(m["rot"]["base"]))
+    d = h @ t[p + "dkv"].T
+    c = rms_norm(d[:, :C], t[p + "dkv.norm"], eps)
+    k_rot = rotate_half(d[:, C:], pos, m["rot"]["dims"], float(m["rot"]["base"]))
+    if past is not None:
+        c, k_rot = torch.cat([past[0], c]), torch.cat([past[1], k_rot])
+    n = c.shape[0]
+    k_plain = (c @ t[p + "uk"].T).view(n, H, D)
+    v = (c @ t[p + "uv"].T).view(n, H, V)
+    s = (torch.einsum("thd,nhd->htn", q_plain, k_plain) + torch.einsum("thr,nr->htn", q_rot, k_rot)) * float(m["scale"])
+    qpos = pos[:, None]
+    kpos = torch.arange(n)[None, :]
+    s = s.masked_fill((kpos > qpos)[None], float("-inf"))
+    sink = t[p + "sink"]
+    mx = torch.maximum(s.max(-1).values, sink[:, None].expand(H, T))
+    e = torch.exp(s - mx[..., None])
+    w = e / (e.sum(-1) + torch.exp(sink[:, None] - mx))[..., None]
+    o = torch.einsum("htn,nhv->thv", w, v).reshape(T, H * V)
+    return o @ t[p + "o"].T, (c, k_rot)
+
+
+def route(h, r: dict, t: Dict[str, torch.Tensor], p: str):
+    """(chosen experts [tokens, top], their weights [tokens, top])."""
+    E, top = r["experts"], r["top"]
+    s = torch.sigmoid(h @ t[p + "router"].T)
+    choice = s + t[p + "correction"]
+    g = r.get("groups")
+    if g:
+        per = E // g["count"]
+        grouped = choice.view(-1, g["count"], per)
+        gs = grouped.topk(min(2, per), dim=-1).values.sum(-1)
+        keep = gs.topk(g["keep"], dim=-1).indices
+        ok = torch.zeros_like(gs, dtype=torch.bool).scatter_(1, keep, True)
+        choice = grouped.masked_fill(~ok[..., None], float("-inf")).reshape(-1, E)
+    idx = choice.topk(top, dim=-1).indices
+    w = s.gather(1, idx)
+    return idx, w / (w.sum(-1, keepdim=True) + 1e-20)
+
+
+def moe(h, mlp: dict, t: Dict[str, torch.Tensor], p: str):
+    idx, w = route(h, mlp["router"], t, p)
+    out = torch.zeros(h.shape[0], t[p + "e0.down"].shape[0], dtype=F)
+    for i in range(h.shape[0]):
+        for j, e in enumerate(idx[i].tolist()):
+            q = f"{p}e{e}."
+            out[i] += w[i, j] * gated(h[i:i + 1], t[q + "gate"], t[q + "up"], t[q + "down"], silu)[0]
+    if mlp.get("shared"):
+        q = p + "shared."
+        out = out + torch.sigmoid(h @ t[q + "sg"].T) * gated(h, t[q + "gate"], t[q + "up"], t[q + "down"], silu)
+    return out
+
+
+def schedule(cfg: dict) -> List[tuple]:
+    """The layer runs in order: (layer, number of the pass if it is the first layer of a pass, else None)."""
+    n = len(cfg["layers"])
+    loop = cfg.get("loop")
+    if not loop:
+        return [(i, None) for i in range(n)]
+    runs = [(i, None) for i in range(loop["start"])]
+    for rep in range(loop["times"]):
+        for i in range(loop["start"], loop["stop"]):
+            runs.append((i, rep if i == loop["start"] else None))
+    return runs + [(i, None) for i in range(loop["stop"], n)]
+
+
+class Plain:
+    """One sequence, fed in pieces: ``feed(tokens)`` returns (logits of these tokens, stream after every layer run)."""
+
+    def __init__(self, cfg: dict, tensors: Dict[str, torch.Tensor]):
+        self.cfg = cfg
+        self.t = {k: f64(v) for k, v in tensors.items()}
+        self.runs = schedule(cfg)
+        self.memory = [None] * len(self.runs)
+        self.n = 0
+
+    def feed(self, tokens):
+        cfg, t = self.cfg, self.t
+        eps = float(cfg["norm"]["eps"])
+        x0 = t["embed"][torch.as_tensor(tokens)] * float(cfg["embedding"]["scale"])
+        x = x0.clone()
+        after = []
+        for r, (i, rep) in enumerate(self.runs):
+            L = cfg["layers"][i]
+            if rep is not None:
+                if rep > 0:
+                    x = x + x0
+                x = x + t["loop.step"][rep]
+            p = f"l{i}."
+            h = layer_norm(x, t[p + "norm1"], t[p + "norm1.b"], eps)
+            if L["type"] == "gla":
+                y, self.memory[r] = gla(h, L["mixer"], t, p + "mix.", eps, self.memory[r])
+            elif L["type"] == "latent_attention":
+                y, self.memory[r] = latent_attention(h, L["mixer"], t, p + "mix.", eps, self.n, self.memory[r])
+            else:
+                raise ValueError(L["type"])
+            x = x + y
+            if L.get("mlp"):
+                h = layer_norm(x, t[p + "norm2"], t[p + "norm2.b"], eps)
+                if L["mlp"]["kind"] == "dense":
+                    y = gated(h, t[p + "mlp.gate"], t[p + "mlp.up"], t[p + "mlp.down"], gelu_tanh)
+                else:
+                    y = moe(h, L["mlp"], t, p + "mlp.")
+                x = x + y
+            after.append(x.clone())
+        self.n += len(tokens)
+        z = layer_norm(x, t["final.norm"], t["final.norm.b"], eps) @ t["head"].T
+        cap = cfg.get("logit_softcap")
+        if cap:
+            z = float(cap) * torch.tanh(z / float(cap))
+        return z, torch.stack(after)

@@ -91,21 +91,22 @@ class Cache:
         for e in sorted(needs):
             need = needs[e]
             if isinstance(need, KVNeed):
-                by_key.setdefault((need.n_kv_heads, need.head_dim, need.window), []).append(e)
+                by_key.setdefault((need.n_kv_heads, need.head_dim, need.window, need.values), []).append(e)
             elif isinstance(need, StateNeed):
                 self.states[e] = torch.zeros((self.max_slots,) + tuple(need.shape), dtype=need.dtype,
                                              device=self.device)
             elif need is not None:
                 raise TypeError(f"schedule entry {e}: a cache need must be KVNeed, StateNeed or None, got {need!r}")
-        for (nkv, hd, window), entries in by_key.items():
+        for (nkv, hd, window, values), entries in by_key.items():
             ring = pages_for(window) * PAGE_ROWS if window else 0
             shape = (len(entries), self.n_pages, nkv, PAGE_ROWS, hd)
             # a ring never holds more than ring_rows per sequence, so its pool can be smaller
             n_pages = min(self.n_pages, self.max_slots * (ring // PAGE_ROWS)) if ring else self.n_pages
             shape = (len(entries), n_pages, nkv, PAGE_ROWS, hd)
-            g = KVGroup(KVNeed(nkv, hd, window), entries, ring, Pool(n_pages, "page"),
-                        torch.empty(shape, dtype=dtype, device=self.device),
-                        torch.empty(shape, dtype=dtype, device=self.device))
+            k_pool = torch.empty(shape, dtype=dtype, device=self.device)
+            # a group without values: ``v`` names the key pool, so that a view of it is never None
+            g = KVGroup(KVNeed(nkv, hd, window, values), entries, ring, Pool(n_pages, "page"), k_pool,
+                        torch.empty(shape, dtype=dtype, device=self.device) if values else k_pool)
             for i, e in enumerate(entries):
                 self.entry_group[e] = (len(self.groups), i)
             self.groups.append(g)
@@ -229,4 +230,4 @@ class Cache:
     def bytes_per_token(self) -> int:
         """Key and value bytes one token adds across all groups (rings add nothing past their size)."""
         es = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(g.entries) * g.need.n_kv_heads * g.need.head_dim * es for g in self.groups)
+        return sum((2 if g.need.values else 1) * len(g.entries) * g.need.n_kv_heads * g.need.head_dim * es for g in self.groups)

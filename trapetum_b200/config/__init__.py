@@ -2,7 +2,8 @@ from .base import (ArchitectureEntry, ConfigError, LayerSpec, ModelSpec, PartSpe
                    architecture_name, known_architectures, load_config, read_config_dict, register_architecture)
 from .divanex import DivanexConfig
 from .gemma2 import Gemma2Config
+from .lofirax import LofiraxConfig
 
-__all__ = ["ArchitectureEntry", "ConfigError", "DivanexConfig", "Gemma2Config", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry",
+__all__ = ["ArchitectureEntry", "ConfigError", "DivanexConfig", "Gemma2Config", "LayerSpec", "LofiraxConfig", "ModelSpec", "PartSpec", "ScheduleEntry",
            "architecture", "architecture_name", "known_architectures", "load_config", "read_config_dict",
            "register_architecture"]

@@ -109,9 +109,12 @@ class ScheduleEntry:
     be named by several entries and then runs with the same weights each time).
     ``cache_of`` names the *entry* whose cache this call uses: itself by
     default (the call appends its own keys and values, or owns its own state),
-    or an earlier entry, whose cache it then only reads."""
+    or an earlier entry, whose cache it then only reads.  ``before`` names a ``stream_input`` part that
+    changes the residual stream right before this call (for instance what a repeated span of layers adds at
+    the start of each pass); None: nothing does."""
     layer: int
     cache_of: Optional[int] = None
+    before: Optional["PartSpec"] = None
 
 
 @dataclass(frozen=True)
@@ -159,7 +162,8 @@ def spec_to_json(spec: "ModelSpec") -> str:
         "embedding": enc(spec.embedding), "final_norm": enc(spec.final_norm), "head": enc(spec.head),
         "layers": [{"prefix": l.prefix, "block": enc(l.block), "mixer": enc(l.mixer), "feed_forward": enc(l.feed_forward)}
                    for l in spec.layers],
-        "schedule": [{"layer": e.layer, "cache_of": e.cache_of} for e in spec.schedule],
+        "schedule": [dict({"layer": e.layer, "cache_of": e.cache_of}, **({"before": enc(e.before)} if e.before else {}))
+                     for e in spec.schedule],
         "max_positions": spec.max_positions, "stop_ids": list(spec.stop_ids)})
 
 

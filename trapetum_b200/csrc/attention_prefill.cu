@@ -36,6 +36,7 @@ struct PrefillArgs {
     bf16* out;                                    // [T, n_heads * HD]
     int n_heads, n_kv_heads, window;
     float scale, cap;
+    const float* sink;                            // [n_heads] or null: the softmax denominator also holds exp(sink_h)
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -229,7 +230,14 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_prefill_mma_kernel(PrefillAr
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
-    const float inv_a = 1.f / l_run[0], inv_b = 1.f / l_run[1];
+    float inv_a = 1.f / l_run[0], inv_b = 1.f / l_run[1];
+    if (a.sink != nullptr) {
+        const float sk = a.sink[h];
+        const float Ma = fmaxf(m_run[0], sk), Mb = fmaxf(m_run[1], sk);
+        const float fa = expf(m_run[0] - Ma), fb = expf(m_run[1] - Mb);
+        inv_a = fa / (l_run[0] * fa + expf(sk - Ma));
+        inv_b = fb / (l_run[1] * fb + expf(sk - Mb));
+    }
     bf16* orow_a = a.out + ((size_t)(s0 + row_a) * a.n_heads + h) * HD;
     bf16* orow_b = a.out + ((size_t)(s0 + row_b) * a.n_heads + h) * HD;
 #pragma unroll
@@ -241,9 +249,10 @@ __global__ void __launch_bounds__(NWARPS * 32) attn_prefill_mma_kernel(PrefillAr
 
 extern "C" int tb_attn_prefill_head_dim() { return HD; }
 
-extern "C" int tb_attn_prefill_mma(const void* q, const void* k, const void* v, long long q_stride, long long kv_stride,
-                                   const int* seq_start, void* out, int batch, int max_seq_len, int n_heads,
-                                   int n_kv_heads, int hd, float scale, float cap, int window, cudaStream_t stream) {
+extern "C" int tb_attn_prefill_mma_ex(const void* q, const void* k, const void* v, long long q_stride, long long kv_stride,
+                                      const int* seq_start, void* out, int batch, int max_seq_len, int n_heads,
+                                      int n_kv_heads, int hd, float scale, float cap, int window, const float* sink,
+                                      cudaStream_t stream) {
     if (batch <= 0 || max_seq_len <= 0) return 0;
     if (hd != HD) return tb_refuse("attn_prefill: this library is built for head_dim %d, got %d", HD, hd);
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads)
@@ -254,7 +263,7 @@ extern "C" int tb_attn_prefill_mma(const void* q, const void* k, const void* v, 
     PrefillArgs a;
     a.q = (const bf16*)q; a.k = (const bf16*)k; a.v = (const bf16*)v;
     a.q_stride = q_stride; a.kv_stride = kv_stride; a.seq_start = seq_start; a.out = (bf16*)out;
-    a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.window = window; a.scale = scale; a.cap = cap;
+    a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.window = window; a.scale = scale; a.cap = cap; a.sink = sink;
     constexpr int SMEM = (BM + 4 * BN) * PITCH;
     static bool attr_set = false;
     if (!attr_set) {
@@ -265,4 +274,11 @@ extern "C" int tb_attn_prefill_mma(const void* q, const void* k, const void* v, 
     dim3 grid((max_seq_len + BM - 1) / BM, n_heads, batch);
     tb_launch(attn_prefill_mma_kernel, dim3(grid), dim3(NWARPS * 32), SMEM, stream, a);
     return tb_launch_status();
+}
+
+extern "C" int tb_attn_prefill_mma(const void* q, const void* k, const void* v, long long q_stride, long long kv_stride,
+                                   const int* seq_start, void* out, int batch, int max_seq_len, int n_heads,
+                                   int n_kv_heads, int hd, float scale, float cap, int window, cudaStream_t stream) {
+    return tb_attn_prefill_mma_ex(q, k, v, q_stride, kv_stride, seq_start, out, batch, max_seq_len, n_heads, n_kv_heads, hd,
+                                  scale, cap, window, nullptr, stream);
 }

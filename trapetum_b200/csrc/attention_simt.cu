@@ -81,7 +81,7 @@ __global__ void attn_prefill_simt_kernel(const T* __restrict__ q, const T* __res
                                          long long q_stride, long long kv_stride,
                                          const int* __restrict__ seq_start, const int* __restrict__ token_seq,
                                          T* __restrict__ out, int n_tokens, int n_heads, int n_kv_heads, int hd,
-                                         float scale, float cap, int window) {
+                                         float scale, float cap, int window, const float* __restrict__ sink) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float smem[];
@@ -107,7 +107,13 @@ __global__ void attn_prefill_simt_kernel(const T* __restrict__ q, const T* __res
         const T* vrow = v + (size_t)(s0 + j) * kv_stride + (size_t)kvh * hd;
         warp_chunk<T, NC>(acc, q_s, valid ? krow : nullptr, valid ? vrow : nullptr, valid, hd, scale, cap, lane);
     }
-    const float inv = 1.f / acc.l;
+    float inv = 1.f / acc.l;
+    if (sink != nullptr) {
+        // a sink: the denominator also holds exp(sink_h), which has no key and no value
+        const float M = fmaxf(acc.m, sink[h]);
+        const float f = expf(acc.m - M);
+        inv = f / (acc.l * f + expf(sink[h] - M));
+    }
     T* orow = out + ((size_t)t * n_heads + h) * hd;
 #pragma unroll
     for (int c = 0; c < NC; c++) {
@@ -239,10 +245,11 @@ static int check_heads(int n_heads, int n_kv_heads, int hd) {
     return 0;
 }
 
-extern "C" int tb_attn_prefill_simt(const void* q, const void* k, const void* v, long long q_stride,
-                                    long long kv_stride, const int* seq_start, const int* token_seq, void* out,
-                                    int dtype, int n_tokens, int n_heads, int n_kv_heads, int hd,
-                                    float scale, float cap, int window, cudaStream_t stream) {
+// ``sink``: [n_heads] 32-bit numbers or null.  With it every head's softmax denominator also holds exp(sink_h).
+extern "C" int tb_attn_prefill_simt_ex(const void* q, const void* k, const void* v, long long q_stride,
+                                       long long kv_stride, const int* seq_start, const int* token_seq, void* out,
+                                       int dtype, int n_tokens, int n_heads, int n_kv_heads, int hd,
+                                       float scale, float cap, int window, const float* sink, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (check_heads(n_heads, n_kv_heads, hd)) return -1;
     const int warps = 4;
@@ -253,8 +260,16 @@ extern "C" int tb_attn_prefill_simt(const void* q, const void* k, const void* v,
     TB_DISPATCH_1(dtype, T, DISPATCH_NC(nc,
         tb_launch(attn_prefill_simt_kernel<T, NC>, dim3(blocks), dim3(warps * 32), smem, stream, 
             (const T*)q, (const T*)k, (const T*)v, q_stride, kv_stride, seq_start, token_seq, (T*)out,
-            n_tokens, n_heads, n_kv_heads, hd, scale, cap, window)));
+            n_tokens, n_heads, n_kv_heads, hd, scale, cap, window, sink)));
     return tb_launch_status();
+}
+
+extern "C" int tb_attn_prefill_simt(const void* q, const void* k, const void* v, long long q_stride,
+                                    long long kv_stride, const int* seq_start, const int* token_seq, void* out,
+                                    int dtype, int n_tokens, int n_heads, int n_kv_heads, int hd,
+                                    float scale, float cap, int window, cudaStream_t stream) {
+    return tb_attn_prefill_simt_ex(q, k, v, q_stride, kv_stride, seq_start, token_seq, out, dtype, n_tokens, n_heads,
+                                   n_kv_heads, hd, scale, cap, window, nullptr, stream);
 }
 
 extern "C" long long tb_attn_decode_scratch_floats(int batch, int n_heads, int hd, int n_splits) {

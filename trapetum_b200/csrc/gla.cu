@@ -1,0 +1,198 @@
+// Gated linear attention: everything between the input products and the output product.
+//
+// Per head, with key channels d and value channels v, for the tokens of a sequence in order:
+//     S[d][v] <- decay_t[d] * S[d][v] + k_t[d] * v_t[v];      o_t[v] = sum_d S[d][v] * q_t[d]
+// where decay_t[d] = sigmoid(z_t[d])^(1/tau) and z_t = A2 (A1 x_t) + bias (a product of low rank).
+// Then every head's o_t is divided by its root mean square over v (+ eps inside the root), multiplied
+// by a weight shared by the heads and by silu(g_t).
+//
+//   tb_gla_decay      z from the 32-bit partial sums of A1 x, the decay as exp(-softplus(-z) / tau)
+//   tb_gla_scan       the recurrence; the state S of every sequence lives in a 32-bit row addressed by
+//                     slot, is read at the start of the step's tokens and written back at their end,
+//                     so a step of whole prompts and a step of one token each are the same kernel
+//   tb_gla_gate_norm  the unit norm, the weight and the gate; output in the activations' dtype
+//
+// 32-bit throughout: z, the decay, the state, o and the norm.  q, k, v and g arrive in the activations'
+// dtype (they are products) and are widened on the way in.
+//
+// The scan: one CTA = 32 value channels of one head of one sequence, eight warps that each own an
+// eighth of the key channels; a thread keeps its part of one column of S in registers.  q, k and the
+// decay of eight tokens at a time are staged in shared memory (every thread of a warp reads the same
+// word: a broadcast); the warps' partial outputs of those eight tokens meet in shared memory once per tile.
+#include "common.cuh"
+
+TB_EXPORT_ERROR()
+
+struct GlaArgs {
+    const void* proj; long long proj_stride;          // [T] rows of q (H*D), k (H*D), v (H*V), g (H*V)
+    const float* a1; int a1_splits; long long a1_split_stride; int rank;   // [splits][T][rank]
+    const float* a2; const float* a2_bias;            // [H*D][rank], [H*D]
+    float inv_tau, q_scale;
+    const float* norm_w; float eps;                   // [V]
+    float* state; long long state_stride;             // [slots][H*D*V]
+    const int* seq_start; const int* token_seq; const int* slot_ids;
+    float* decay;                                     // [T][H*D] scratch
+    float* y;                                         // [T][H*V] scratch
+    void* out;                                        // [T][H*V]
+    int heads, D, V, batch, n_tokens;
+};
+
+__global__ void gla_decay_kernel(GlaArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float low_s[];                  // [rank]: A1 x of this token
+    const int t = blockIdx.x;
+    const int HD = a.heads * a.D;
+    for (int r = threadIdx.x; r < a.rank; r += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < a.a1_splits; s++) v += a.a1[(size_t)s * a.a1_split_stride + (size_t)t * a.rank + r];
+        low_s[r] = v;
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < HD; c += blockDim.x) {
+        const float* w = a.a2 + (size_t)c * a.rank;
+        float z = 0.f;
+        for (int r = 0; r < a.rank; r++) z = fmaf(w[r], low_s[r], z);
+        z += a.a2_bias[c];
+        const float x = -z;                           // log sigmoid(z) = -softplus(-z)
+        const float sp = x > 20.f ? x : log1pf(expf(x));
+        a.decay[(size_t)t * HD + c] = expf(-sp * a.inv_tau);
+    }
+}
+
+constexpr int GLA_TT = 8;          // tokens per tile
+constexpr int GLA_WARPS = 8;       // slices of the key channels
+
+template <typename T, int DPT>
+__global__ void __launch_bounds__(GLA_WARPS * 32) gla_scan_kernel(GlaArgs a) {
+    pdl_launch_dependents();
+    constexpr int DP = DPT * GLA_WARPS;                // key channels, padded
+    __shared__ float q_s[GLA_TT][DP], k_s[GLA_TT][DP], d_s[GLA_TT][DP];
+    __shared__ float v_s[GLA_TT][32];
+    __shared__ float part_s[GLA_TT][GLA_WARPS][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int D = a.D, V = a.V, HD = a.heads * D, HV = a.heads * V;
+    const int v0 = blockIdx.x * 32, vch = v0 + lane;
+    const bool v_ok = vch < V;
+    pdl_wait();
+    const int s0 = a.seq_start[b], s1 = a.seq_start[b + 1];
+    float* st = a.state + (size_t)a.slot_ids[b] * a.state_stride + (size_t)h * D * V;
+    float S[DPT];
+#pragma unroll
+    for (int j = 0; j < DPT; j++) {
+        const int d = warp * DPT + j;
+        S[j] = (d < D && v_ok) ? st[(size_t)d * V + vch] : 0.f;
+    }
+    const T* proj = (const T*)a.proj;
+    for (int t0 = s0; t0 < s1; t0 += GLA_TT) {
+        const int nt = min(GLA_TT, s1 - t0);
+        for (int i = threadIdx.x; i < GLA_TT * DP; i += blockDim.x) {
+            const int tt = i / DP, d = i % DP;
+            float q = 0.f, k = 0.f, dec = 1.f;
+            if (tt < nt && d < D) {
+                const T* row = proj + (size_t)(t0 + tt) * a.proj_stride;
+                q = to_f<T>(row[h * D + d]) * a.q_scale;
+                k = to_f<T>(row[HD + h * D + d]);
+                dec = a.decay[(size_t)(t0 + tt) * HD + h * D + d];
+            }
+            q_s[tt][d] = q; k_s[tt][d] = k; d_s[tt][d] = dec;
+        }
+        {
+            const int tt = threadIdx.x >> 5;           // 8 warps = 8 tokens of the tile
+            v_s[tt][lane] = (tt < nt && v_ok) ? to_f<T>(proj[(size_t)(t0 + tt) * a.proj_stride + 2 * HD + h * V + vch]) : 0.f;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; tt++) {
+            const float vv = v_s[tt][lane];
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < DPT; j++) {
+                const int d = warp * DPT + j;
+                S[j] = fmaf(d_s[tt][d], S[j], k_s[tt][d] * vv);
+                acc = fmaf(S[j], q_s[tt][d], acc);
+            }
+            part_s[tt][warp][lane] = acc;
+        }
+        __syncthreads();
+        {
+            const int tt = warp;
+            if (tt < nt && v_ok) {
+                float o = 0.f;
+#pragma unroll
+                for (int w = 0; w < GLA_WARPS; w++) o += part_s[tt][w][lane];
+                a.y[(size_t)(t0 + tt) * HV + h * V + vch] = o;
+            }
+        }
+        // the next tile's staging writes q_s..v_s, which nobody reads any more; part_s is written again only
+        // after the next barrier
+    }
+#pragma unroll
+    for (int j = 0; j < DPT; j++) {
+        const int d = warp * DPT + j;
+        if (d < D && v_ok) st[(size_t)d * V + vch] = S[j];
+    }
+}
+
+template <typename T>
+__global__ void gla_gate_norm_kernel(GlaArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long long)a.n_tokens * a.heads) return;
+    const int t = (int)(item / a.heads), h = (int)(item % a.heads);
+    const int V = a.V, HV = a.heads * V, HD = a.heads * a.D;
+    const float* y = a.y + (size_t)t * HV + (size_t)h * V;
+    float sq = 0.f;
+    for (int v = lane; v < V; v += 32) sq = fmaf(y[v], y[v], sq);
+    const float r = 1.f / sqrtf(warp_sum(sq) / (float)V + a.eps);
+    const T* g = (const T*)a.proj + (size_t)t * a.proj_stride + 2 * HD + HV + (size_t)h * V;
+    T* o = (T*)a.out + (size_t)t * HV + (size_t)h * V;
+    for (int v = lane; v < V; v += 32) {
+        const float gv = to_f<T>(g[v]);
+        o[v] = from_f<T>(y[v] * r * a.norm_w[v] * (gv / (1.f + expf(-gv))));
+    }
+}
+
+static int check(const GlaArgs& a) {
+    if (a.heads <= 0 || a.D <= 0 || a.V <= 0 || a.rank <= 0) return tb_refuse("gla: heads=%d D=%d V=%d rank=%d", a.heads, a.D, a.V, a.rank);
+    if (a.D > 256) return tb_refuse("gla: %d key channels per head; the scan keeps up to 256", a.D);
+    if (a.heads > 65535 || a.batch > 65535) return tb_refuse("gla: %d heads x %d sequences exceed one launch", a.heads, a.batch);
+    return 0;
+}
+
+extern "C" int tb_gla_decay(const GlaArgs* args, cudaStream_t stream) {
+    if (args->n_tokens <= 0) return 0;
+    if (check(*args)) return -1;
+    if (args->rank > 4096) return tb_refuse("gla: rank %d", args->rank);
+    tb_launch(gla_decay_kernel, dim3(args->n_tokens), dim3(256), (size_t)args->rank * sizeof(float), stream, *args);
+    return tb_launch_status();
+}
+
+extern "C" int tb_gla_scan(const GlaArgs* args, int dtype, cudaStream_t stream) {
+    if (args->n_tokens <= 0 || args->batch <= 0) return 0;
+    if (check(*args)) return -1;
+    const GlaArgs& a = *args;
+    int dpt = 1;
+    while (dpt * GLA_WARPS < a.D) dpt <<= 1;
+    dim3 grid((a.V + 31) / 32, a.heads, a.batch);
+#define GLA_SCAN(N) TB_DISPATCH_1(dtype, T, tb_launch(gla_scan_kernel<T, N>, dim3(grid), dim3(GLA_WARPS * 32), 0, stream, a))
+    switch (dpt) {
+    case 1: GLA_SCAN(1); break;
+    case 2: GLA_SCAN(2); break;
+    case 4: GLA_SCAN(4); break;
+    case 8: GLA_SCAN(8); break;
+    case 16: GLA_SCAN(16); break;
+    default: GLA_SCAN(32); break;
+    }
+    return tb_launch_status();
+}
+
+extern "C" int tb_gla_gate_norm(const GlaArgs* args, int dtype, cudaStream_t stream) {
+    if (args->n_tokens <= 0) return 0;
+    if (check(*args)) return -1;
+    const long long items = (long long)args->n_tokens * args->heads;
+    TB_DISPATCH_1(dtype, T, tb_launch(gla_gate_norm_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, *args));
+    return tb_launch_status();
+}

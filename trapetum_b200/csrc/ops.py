@@ -1096,3 +1096,309 @@ def attn_decode(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, h
         raise KernelError("attention: this shape's decode kernel does not rotate by itself")
     return attn_decode_simt(q, k_pool, v_pool, page_table, len_after, n_heads, n_kv_heads, head_dim, scale,
                             softcap, window, ring_rows, splits)
+
+
+# ---------------------------------------------------------------------------
+# Layer norm, row-wise additions
+# ---------------------------------------------------------------------------
+def add_layernorm(h: torch.Tensor, a: Optional[torch.Tensor], w: torch.Tensor, b: torch.Tensor, eps: float,
+                  out_dtype: torch.dtype) -> torch.Tensor:
+    """``h += a`` in place (skipped if ``a`` is None), then returns the layer norm of ``h`` with weight and bias.
+    ``h`` float32 [rows, width]; ``a`` [rows, width] or float32 partial sums [splits, rows, width]; ``w``, ``b``
+    float32 [width]."""
+    _cuda(h, a, w, b)
+    if h.dtype != torch.float32 or h.dim() != 2 or not h.is_contiguous():
+        raise KernelError("add_layernorm: the residual stream must be contiguous float32 [rows, width]")
+    n_splits, split_stride, a_code = 1, 0, 0
+    if a is not None:
+        if a.dim() == 3:
+            if a.dtype != torch.float32:
+                raise KernelError("add_layernorm: partial sums must be float32")
+            n_splits, split_stride = a.shape[0], a.stride(0)
+            if tuple(a.shape[1:]) != tuple(h.shape) or a.stride(1) != h.shape[1] or a.stride(2) != 1:
+                raise KernelError(f"add_layernorm: partial sums {tuple(a.shape)} do not fit the stream {tuple(h.shape)}")
+        elif a.shape != h.shape or not a.is_contiguous():
+            raise KernelError(f"add_layernorm: branch {tuple(a.shape)} does not fit the stream {tuple(h.shape)}")
+        a_code = code(a.dtype)
+    for name, t in (("weight", w), ("bias", b)):
+        if t.dtype != torch.float32 or t.numel() != h.shape[1] or not t.is_contiguous():
+            raise KernelError(f"add_layernorm: the {name} must be contiguous float32 [{h.shape[1]}]")
+    out = torch.empty(h.shape, dtype=out_dtype, device=h.device)
+    lib = build.load("layernorm")
+    _check(lib, lib.tb_add_layernorm(_ptr(h), _ptr(a), c_int(a_code), c_int(n_splits), c_longlong(split_stride), _ptr(w),
+                                     _ptr(b), c_float(eps), _ptr(out), c_int(code(out_dtype)), c_int(h.shape[0]),
+                                     c_int(h.shape[1]), _stream()), "add_layernorm")
+    return out
+
+
+def add_rows(h: torch.Tensor, rows: Optional[torch.Tensor], vector: Optional[torch.Tensor]) -> None:
+    """``h += rows + vector`` in place: ``rows`` float32 of h's shape, ``vector`` float32 [width]; either may be None."""
+    _cuda(h, rows, vector)
+    if h.dtype != torch.float32 or h.dim() != 2 or not h.is_contiguous():
+        raise KernelError("add_rows: the residual stream must be contiguous float32 [rows, width]")
+    if rows is not None and (rows.dtype != torch.float32 or rows.shape != h.shape or not rows.is_contiguous()):
+        raise KernelError("add_rows: rows must be contiguous float32 of the stream's shape")
+    if vector is not None and (vector.dtype != torch.float32 or vector.numel() != h.shape[1] or not vector.is_contiguous()):
+        raise KernelError("add_rows: the vector must be contiguous float32 [width]")
+    lib = build.load("layernorm")
+    _check(lib, lib.tb_add_rows(_ptr(h), _ptr(rows), _ptr(vector), c_int(h.shape[0]), c_int(h.shape[1]), _stream()), "add_rows")
+
+
+# ---------------------------------------------------------------------------
+# Gated linear attention
+# ---------------------------------------------------------------------------
+class _GlaArgs(ctypes.Structure):
+    _fields_ = [("proj", c_void_p), ("proj_stride", c_longlong),
+                ("a1", c_void_p), ("a1_splits", c_int), ("a1_split_stride", c_longlong), ("rank", c_int),
+                ("a2", c_void_p), ("a2_bias", c_void_p), ("inv_tau", c_float), ("q_scale", c_float),
+                ("norm_w", c_void_p), ("eps", c_float), ("state", c_void_p), ("state_stride", c_longlong),
+                ("seq_start", c_void_p), ("token_seq", c_void_p), ("slot_ids", c_void_p),
+                ("decay", c_void_p), ("y", c_void_p), ("out", c_void_p),
+                ("heads", c_int), ("D", c_int), ("V", c_int), ("batch", c_int), ("n_tokens", c_int)]
+
+
+def gla(proj: torch.Tensor, low: torch.Tensor, a2: torch.Tensor, a2_bias: torch.Tensor, tau: float, q_scale: float,
+        norm_w: torch.Tensor, eps: float, heads: int, key_dim: int, value_dim: int, state: torch.Tensor,
+        seq_start: torch.Tensor, token_seq: torch.Tensor, slot_ids: torch.Tensor, batch: int) -> torch.Tensor:
+    """Gated linear attention between its products (see gla.cu).  ``proj`` [T, 2 H D + 2 H V]: q, k, v and the output
+    gate's pre-activation, in the compute dtype; ``low`` float32 [splits, T, rank]: partial sums of the decay's first
+    product; ``a2`` float32 [H D, rank], ``a2_bias`` float32 [H D], ``norm_w`` float32 [V]; ``state`` float32
+    [slots, H D V], rows picked by ``slot_ids``, read and written.  Returns [T, H V] in the compute dtype."""
+    _cuda(proj, low, a2, a2_bias, norm_w, state, seq_start, token_seq, slot_ids)
+    _rows_contig(proj, "gla: proj")
+    T = proj.shape[0]
+    HD, HV = heads * key_dim, heads * value_dim
+    if proj.shape[1] != 2 * HD + 2 * HV:
+        raise KernelError(f"gla: the input product has {proj.shape[1]} columns, the sizes ask for {2 * HD + 2 * HV}")
+    if low.dim() == 2:
+        low = low[None]
+    rank = low.shape[2]
+    if low.dtype != torch.float32 or low.shape[1] != T or low.stride(2) != 1 or low.stride(1) != rank:
+        raise KernelError(f"gla: the decay's first product must be float32 [splits, {T}, rank], got {tuple(low.shape)} {low.dtype}")
+    for name, t, shape in (("a2", a2, (HD, rank)), ("a2 bias", a2_bias, (HD,)), ("norm", norm_w, (value_dim,))):
+        if tuple(t.shape) != shape or t.dtype != torch.float32 or not t.is_contiguous():
+            raise KernelError(f"gla: {name} must be contiguous float32 {shape}, got {tuple(t.shape)} {t.dtype}")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] != HD * value_dim:
+        raise KernelError(f"gla: the state must be float32 [slots, {HD * value_dim}]")
+    dt = proj.dtype
+    decay = torch.empty((T, HD), dtype=torch.float32, device=proj.device)
+    y = torch.empty((T, HV), dtype=torch.float32, device=proj.device)
+    out = torch.empty((T, HV), dtype=dt, device=proj.device)
+    a = _GlaArgs()
+    a.proj = proj.data_ptr(); a.proj_stride = proj.stride(0)
+    a.a1 = low.data_ptr(); a.a1_splits = low.shape[0]; a.a1_split_stride = low.stride(0); a.rank = rank
+    a.a2 = a2.data_ptr(); a.a2_bias = a2_bias.data_ptr(); a.inv_tau = 1.0 / tau; a.q_scale = q_scale
+    a.norm_w = norm_w.data_ptr(); a.eps = eps; a.state = state.data_ptr(); a.state_stride = state.stride(0)
+    a.seq_start = seq_start.data_ptr(); a.token_seq = token_seq.data_ptr(); a.slot_ids = slot_ids.data_ptr()
+    a.decay = decay.data_ptr(); a.y = y.data_ptr(); a.out = out.data_ptr()
+    a.heads = heads; a.D = key_dim; a.V = value_dim; a.batch = batch; a.n_tokens = T
+    lib = build.load("gla")
+    _check(lib, lib.tb_gla_decay(ctypes.byref(a), _stream()), "gla_decay")
+    _check(lib, lib.tb_gla_scan(ctypes.byref(a), c_int(code(dt)), _stream()), "gla_scan")
+    _check(lib, lib.tb_gla_gate_norm(ctypes.byref(a), c_int(code(dt)), _stream()), "gla_gate_norm")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Attention over cached latent rows
+# ---------------------------------------------------------------------------
+class _LatentRowsArgs(ctypes.Structure):
+    _fields_ = [("dkv", c_void_p), ("splits", c_int), ("split_stride", c_longlong), ("norm_w", c_void_p), ("eps", c_float),
+                ("inv_freq", c_void_p), ("rot_dims", c_int), ("C", c_int), ("R", c_int), ("n_tokens", c_int),
+                ("positions", c_void_p), ("token_seq", c_void_p), ("page_table", c_void_p), ("pt_stride", c_int),
+                ("page_rows", c_int), ("pool", c_void_p), ("rows", c_void_p)]
+
+
+def latent_rows(part: torch.Tensor, norm_w: torch.Tensor, eps: float, inv_freq: Optional[torch.Tensor], rot_dims: int,
+                C: int, R: int, positions: torch.Tensor, token_seq: torch.Tensor, pool: torch.Tensor,
+                page_table: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """From the down projection's partial sums ``part`` float32 [splits, T, C + R] to the cached rows: the first C
+    columns RMS-normed times ``norm_w``, the last R rotated at the token's position; written to the paged ``pool``
+    [pages, 1, PAGE_ROWS, C + R] and returned packed [T, C + R], both in ``out_dtype``."""
+    _cuda(part, norm_w, inv_freq, positions, token_seq, pool, page_table)
+    if part.dim() == 2:
+        part = part[None]
+    T = part.shape[1]
+    if part.dtype != torch.float32 or part.shape[2] != C + R or part.stride(2) != 1 or part.stride(1) != C + R:
+        raise KernelError(f"latent_rows: partial sums must be float32 [splits, T, {C + R}], got {tuple(part.shape)}")
+    if norm_w.dtype != torch.float32 or norm_w.numel() != C or not norm_w.is_contiguous():
+        raise KernelError(f"latent_rows: the norm weight must be contiguous float32 [{C}]")
+    if rot_dims and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2):
+        raise KernelError("latent_rows: inv_freq must be float32 [rot_dims / 2]")
+    if pool.dtype != out_dtype or not pool.is_contiguous() or pool.shape[-1] != C + R or pool.shape[-2] != PAGE_ROWS \
+            or (pool.dim() == 4 and pool.shape[1] != 1):
+        raise KernelError(f"latent_rows: the pool must be contiguous {out_dtype} [pages, 1, {PAGE_ROWS}, {C + R}]")
+    rows = torch.empty((T, C + R), dtype=out_dtype, device=part.device)
+    a = _LatentRowsArgs()
+    a.dkv = part.data_ptr(); a.splits = part.shape[0]; a.split_stride = part.stride(0)
+    a.norm_w = norm_w.data_ptr(); a.eps = eps
+    a.inv_freq = inv_freq.data_ptr() if rot_dims else None; a.rot_dims = rot_dims
+    a.C = C; a.R = R; a.n_tokens = T
+    a.positions = positions.data_ptr(); a.token_seq = token_seq.data_ptr()
+    a.page_table = page_table.data_ptr(); a.pt_stride = page_table.stride(0); a.page_rows = PAGE_ROWS
+    a.pool = pool.data_ptr(); a.rows = rows.data_ptr()
+    lib = build.load("attention_latent")
+    _check(lib, lib.tb_latent_rows(ctypes.byref(a), c_int(code(out_dtype)), _stream()), "latent_rows")
+    return rows
+
+
+def head_linear(x: torch.Tensor, w: torch.Tensor, heads: int) -> torch.Tensor:
+    """``y[t, h, :] = w[h] @ x[t, h, :]`` for ``x`` [T, heads * in] (rows may be a column slice) and ``w`` [heads, out, in]
+    of x's dtype; returns [T, heads * out]."""
+    _cuda(x, w)
+    _rows_contig(x, "head_linear: x")
+    if w.dim() != 3 or w.shape[0] != heads or not w.is_contiguous() or w.dtype != x.dtype or x.shape[1] != heads * w.shape[2]:
+        raise KernelError(f"head_linear: x {tuple(x.shape)} {x.dtype} and w {tuple(w.shape)} {w.dtype} do not fit {heads} heads")
+    T, out_dim, in_dim = x.shape[0], w.shape[1], w.shape[2]
+    y = torch.empty((T, heads * out_dim), dtype=x.dtype, device=x.device)
+    lib = build.load("attention_latent")
+    _check(lib, lib.tb_head_linear(_ptr(x), c_longlong(x.stride(0)), _ptr(w), _ptr(y), c_longlong(y.stride(0)),
+                                   c_int(code(x.dtype)), c_int(T), c_int(heads), c_int(in_dim), c_int(out_dim), _stream()),
+           "head_linear")
+    return y
+
+
+class _LatentDecodeArgs(ctypes.Structure):
+    _fields_ = [("q", c_void_p), ("q_stride", c_longlong), ("pool", c_void_p), ("page_table", c_void_p), ("pt_stride", c_int),
+                ("page_rows", c_int), ("len_after", c_void_p), ("sink", c_void_p), ("out", c_void_p), ("out_stride", c_longlong),
+                ("partial", c_void_p), ("heads", c_int), ("C", c_int), ("R", c_int), ("out_dim", c_int), ("n_splits", c_int),
+                ("scale", c_float)]
+
+
+def latent_decode(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, len_after: torch.Tensor,
+                  sink: Optional[torch.Tensor], heads: int, C: int, R: int, scale: float, len_bucket: int) -> torch.Tensor:
+    """One mapped query [heads * (C + R)] per sequence against its cached rows; returns [batch, heads * C] (the weighted
+    sums of the rows' first C columns).  ``len_bucket``: an upper bound of the longest context, which the number of
+    pieces a sequence is cut into depends on (and nothing else does, so that a captured step stays valid)."""
+    _cuda(q, pool, page_table, len_after, sink)
+    _rows_contig(q, "latent_decode: q")
+    B = q.shape[0]
+    if q.shape[1] != heads * (C + R) or pool.dtype != q.dtype:
+        raise KernelError(f"latent_decode: q {tuple(q.shape)} does not fit {heads} heads of {C + R}")
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != heads or not sink.is_contiguous()):
+        raise KernelError(f"latent_decode: the sink must be contiguous float32 [{heads}]")
+    pieces = max(1, min((len_bucket + 255) // 256, max(1, (2 * sm_count(q.device)) // max(1, B * heads))))
+    out = torch.empty((B, heads * C), dtype=q.dtype, device=q.device)
+    scratch = torch.empty(B * heads * pieces * (C + 2), dtype=torch.float32, device=q.device) if pieces > 1 else None
+    a = _LatentDecodeArgs()
+    a.q = q.data_ptr(); a.q_stride = q.stride(0); a.pool = pool.data_ptr()
+    a.page_table = page_table.data_ptr(); a.pt_stride = page_table.stride(0); a.page_rows = PAGE_ROWS
+    a.len_after = len_after.data_ptr(); a.sink = sink.data_ptr() if sink is not None else None
+    a.out = out.data_ptr(); a.out_stride = out.stride(0); a.partial = scratch.data_ptr() if scratch is not None else None
+    a.heads = heads; a.C = C; a.R = R; a.out_dim = C; a.n_splits = pieces; a.scale = scale
+    lib = build.load("attention_latent")
+    _check(lib, lib.tb_latent_decode(ctypes.byref(a), c_int(code(q.dtype)), c_int(B), _stream()), "latent_decode",
+           2 if pieces > 1 else 1)
+    return out
+
+
+def attn_prefill_sink(q, k, v, seq_start, token_seq, n_heads, head_dim, scale, sink, max_seq_len) -> torch.Tensor:
+    """Causal prefill attention of packed sequences, one kv head per query head, whose softmax denominators also
+    hold ``exp(sink[h])`` (``sink`` float32 [n_heads], or None).  bfloat16 with a head size the tensor-core kernel
+    takes runs there, everything else on the generic kernel."""
+    _cuda(q, k, v, seq_start, token_seq, sink)
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _rows_contig(t, "attention: " + name)
+    if k.stride(0) != v.stride(0) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise KernelError("attention: k and v must share row stride and dtype with q")
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != n_heads or not sink.is_contiguous()):
+        raise KernelError(f"attention: the sink must be contiguous float32 [{n_heads}]")
+    T = q.shape[0]
+    out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    aligned = all(t.data_ptr() % 16 == 0 and t.stride(0) % 8 == 0 for t in (q, k, v))
+    if attn_prefill_takes(q.dtype, head_dim) and aligned:
+        lib = build.load(attn_prefill_lib(head_dim))
+        B = seq_start.numel() - 1
+        _check(lib, lib.tb_attn_prefill_mma_ex(_ptr(q), _ptr(k), _ptr(v), c_longlong(q.stride(0)), c_longlong(k.stride(0)),
+                                               _ptr(seq_start), _ptr(out), c_int(B), c_int(max_seq_len), c_int(n_heads),
+                                               c_int(n_heads), c_int(head_dim), c_float(scale), c_float(0.0), c_int(0),
+                                               _ptr(sink), _stream()), "attn_prefill_mma")
+        return out
+    lib = build.load("attention_simt")
+    _check(lib, lib.tb_attn_prefill_simt_ex(_ptr(q), _ptr(k), _ptr(v), c_longlong(q.stride(0)), c_longlong(k.stride(0)),
+                                            _ptr(seq_start), _ptr(token_seq), _ptr(out), c_int(code(q.dtype)), c_int(T),
+                                            c_int(n_heads), c_int(n_heads), c_int(head_dim), c_float(scale), c_float(0.0),
+                                            c_int(0), _ptr(sink), _stream()), "attn_prefill_simt")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Experts behind a router
+# ---------------------------------------------------------------------------
+class _MoeRouteArgs(ctypes.Structure):
+    _fields_ = [("x", c_void_p), ("x_stride", c_longlong), ("router", c_void_p), ("correction", c_void_p),
+                ("shared_gate", c_void_p), ("idx", c_void_p), ("weight", c_void_p), ("gate", c_void_p),
+                ("n_tokens", c_int), ("W", c_int), ("E", c_int), ("top", c_int), ("groups", c_int), ("keep", c_int),
+                ("group_top", c_int), ("weight_eps", c_float)]
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], shared_gate: Optional[torch.Tensor],
+              top: int, groups: int, keep: int, group_top: int, weight_eps: float):
+    """Sigmoid-scored routing with groups (see moe.cu).  Returns (chosen experts int32 [T, top], their weights float32
+    [T, top], the shared expert's gate float32 [T] or None)."""
+    _cuda(x, router, correction, shared_gate)
+    _rows_contig(x, "moe_route: x")
+    T, W = x.shape
+    E = router.shape[0]
+    if router.dim() != 2 or router.shape[1] != W or not router.is_contiguous():
+        raise KernelError(f"moe_route: the router must be contiguous [experts, {W}]")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != E or not correction.is_contiguous()):
+        raise KernelError(f"moe_route: the correction must be contiguous float32 [{E}]")
+    if shared_gate is not None and (shared_gate.dtype != router.dtype or shared_gate.numel() != W or not shared_gate.is_contiguous()):
+        raise KernelError(f"moe_route: the shared gate must be contiguous [{W}] of the router's dtype")
+    idx = torch.empty((T, top), dtype=torch.int32, device=x.device)
+    weight = torch.empty((T, top), dtype=torch.float32, device=x.device)
+    gate = torch.empty((T,), dtype=torch.float32, device=x.device) if shared_gate is not None else None
+    a = _MoeRouteArgs()
+    a.x = x.data_ptr(); a.x_stride = x.stride(0); a.router = router.data_ptr()
+    a.correction = correction.data_ptr() if correction is not None else None
+    a.shared_gate = shared_gate.data_ptr() if shared_gate is not None else None
+    a.idx = idx.data_ptr(); a.weight = weight.data_ptr(); a.gate = gate.data_ptr() if gate is not None else None
+    a.n_tokens = T; a.W = W; a.E = E; a.top = top; a.groups = groups; a.keep = keep; a.group_top = group_top
+    a.weight_eps = weight_eps
+    lib = build.load("moe")
+    _check(lib, lib.tb_moe_route(ctypes.byref(a), c_int(code(x.dtype)), c_int(code(router.dtype)), _stream()), "moe_route")
+    return idx, weight, gate
+
+
+class _MoeExpertArgs(ctypes.Structure):
+    _fields_ = [("x", c_void_p), ("x_stride", c_longlong), ("gate_w", c_void_p), ("up_w", c_void_p), ("down_w", c_void_p),
+                ("idx", c_void_p), ("weight", c_void_p), ("act", c_void_p), ("shared", c_void_p), ("shared_splits", c_int),
+                ("shared_split_stride", c_longlong), ("gate", c_void_p), ("out", c_void_p),
+                ("n_tokens", c_int), ("W", c_int), ("ff", c_int), ("top", c_int)]
+
+
+def moe_experts(x: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor, down_w: torch.Tensor, idx: torch.Tensor,
+                weight: torch.Tensor, shared: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The weighted sum of every token's chosen experts ``down_e(silu(gate_e x) * up_e x)`` plus ``gate[t] * shared[t]``
+    (``shared`` float32 partial sums [splits, T, W]); returns float32 [T, W].  Expert matrices: ``gate_w``, ``up_w``
+    [E, ff, W] and ``down_w`` [E, W, ff] of x's dtype."""
+    _cuda(x, gate_w, up_w, down_w, idx, weight, shared, gate)
+    _rows_contig(x, "moe: x")
+    T, W = x.shape
+    E, ff = gate_w.shape[0], gate_w.shape[1]
+    top = idx.shape[1]
+    for name, t, shape in (("gate", gate_w, (E, ff, W)), ("up", up_w, (E, ff, W)), ("down", down_w, (E, W, ff))):
+        if tuple(t.shape) != shape or t.dtype != x.dtype or not t.is_contiguous():
+            raise KernelError(f"moe: the experts' {name} matrices must be contiguous {x.dtype} {shape}, got {tuple(t.shape)} {t.dtype}")
+    if shared is not None:
+        if shared.dim() == 2:
+            shared = shared[None]
+        if shared.dtype != torch.float32 or tuple(shared.shape[1:]) != (T, W) or shared.stride(2) != 1 or shared.stride(1) != W \
+                or gate is None:
+            raise KernelError("moe: the shared expert's output must be float32 [splits, T, W] and come with its gate")
+    act = torch.empty((T * top, ff), dtype=x.dtype, device=x.device)
+    out = torch.empty((T, W), dtype=torch.float32, device=x.device)
+    a = _MoeExpertArgs()
+    a.x = x.data_ptr(); a.x_stride = x.stride(0)
+    a.gate_w = gate_w.data_ptr(); a.up_w = up_w.data_ptr(); a.down_w = down_w.data_ptr()
+    a.idx = idx.data_ptr(); a.weight = weight.data_ptr(); a.act = act.data_ptr()
+    a.shared = shared.data_ptr() if shared is not None else None
+    a.shared_splits = shared.shape[0] if shared is not None else 0
+    a.shared_split_stride = shared.stride(0) if shared is not None else 0
+    a.gate = gate.data_ptr() if gate is not None else None
+    a.out = out.data_ptr(); a.n_tokens = T; a.W = W; a.ff = ff; a.top = top
+    lib = build.load("moe")
+    _check(lib, lib.tb_moe_gate_up(ctypes.byref(a), c_int(code(x.dtype)), _stream()), "moe_gate_up")
+    _check(lib, lib.tb_moe_down(ctypes.byref(a), c_int(code(x.dtype)), _stream()), "moe_down")
+    return out

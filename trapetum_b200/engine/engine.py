@@ -71,7 +71,8 @@ class Engine:
         # CUDA graphs for decode steps: only if every part says that its launches depend on nothing
         # that lives on the host (a part that reads ctx.slots in Python, for one, does not qualify)
         self.use_graphs = use_graphs and self.rt.device.type == "cuda"
-        self._graph_safe = all(getattr(p, "graph_safe", False) for b in model.blocks for p in (b, b.mixer, b.feed_forward))
+        self._graph_safe = all(getattr(p, "graph_safe", False) for b in model.blocks for p in (b, b.mixer, b.feed_forward)) \
+            and all(getattr(p, "graph_safe", False) for p in getattr(model, "inputs", {}).values())
         self._decode: Dict[tuple, "_DecodeShape"] = {}
         self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs and self._graph_safe else None
 

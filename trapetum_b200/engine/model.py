@@ -34,9 +34,13 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm, "", rt)
         self.head = build_part("head", spec.head, "", rt)
         self.vocab_size = spec.vocab_size
+        # what schedule entries add to the stream before their layer runs (entry -> part)
+        self.inputs = {e: build_part("stream_input", ent.before, "", rt)
+                       for e, ent in enumerate(spec.schedule) if ent.before is not None}
+        self._keep_embedding = any(p.needs_embedding for p in self.inputs.values())
 
     def parts(self):
-        return [self.embedding] + self.blocks + [self.final_norm, self.head]
+        return [self.embedding] + self.blocks + list(self.inputs.values()) + [self.final_norm, self.head]
 
     # -- weights ----------------------------------------------------------------
     def tensor_specs(self) -> Dict[str, TensorSpec]:
@@ -75,9 +79,13 @@ class Model:
     def forward(self, ids: torch.Tensor, ctx, cache, want_rows: Optional[torch.Tensor]) -> torch.Tensor:
         """``ids`` int32 [tokens]; returns float32 logits [wanted rows, vocab]
         (all rows if ``want_rows`` is None)."""
-        stream = ResidualStream(self.embedding.forward(ids))
+        embedded = self.embedding.forward(ids)
+        # the stream is changed in place: a part that wants the embedding's output later gets a copy of its own
+        stream = ResidualStream(embedded.clone() if self._keep_embedding else embedded)
         for e, ent in enumerate(self.spec.schedule):
             owner = e if ent.cache_of is None else ent.cache_of
+            if e in self.inputs:
+                self.inputs[e].forward(stream, embedded if self._keep_embedding else None, ctx)
             self.blocks[ent.layer].forward(stream, ctx, cache.view(e, owner))
         h = stream.value()
         if want_rows is not None:

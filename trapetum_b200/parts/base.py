@@ -15,7 +15,8 @@ block              the arrangement of a layer's parts around the residual
                    stream (:class:`Block`)
 =================  ==========================================================
 
-plus ``embedding`` and ``head`` at the two ends of the model.  No part knows
+plus ``embedding`` and ``head`` at the two ends of the model, and ``stream_input``
+for what a schedule entry adds to the stream before its layer runs.  No part knows
 which model it is in: sizes, constants and tensor names all arrive as
 parameters.  Registering a new kind needs no change to this package::
 
@@ -47,10 +48,12 @@ class Runtime:
 @dataclass(frozen=True)
 class KVNeed:
     """Keys and values per token.  ``window`` None: all of them are kept;
-    an integer: only the last ``window`` tokens are ever read."""
+    an integer: only the last ``window`` tokens are ever read.  ``values`` False: one row per token is all the
+    mixer keeps (a latent from which it makes keys and values itself), so no value pool is allocated."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    values: bool = True
 
 
 @dataclass(frozen=True)
@@ -136,6 +139,14 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class StreamInput(Part):
+    """Something that changes the residual stream between two layer calls (a schedule entry's ``before``)."""
+    needs_embedding = False      # True: ``forward`` wants the embedding's output as it was before the first layer
+
+    def forward(self, stream, embedded: Optional[torch.Tensor], ctx) -> None:
+        raise NotImplementedError
+
+
 class Block(Part):
     """Arranges a mixer and a feed-forward around the residual stream."""
 
@@ -152,7 +163,7 @@ class Block(Part):
 # Registries
 # ---------------------------------------------------------------------------
 
-_KINDS = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
+_KINDS = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head", "stream_input")
 _REGISTRY: Dict[str, Dict[str, Callable]] = {k: {} for k in _KINDS}
 
 

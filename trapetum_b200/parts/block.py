@@ -70,14 +70,24 @@ class SandwichBlock(_NormedBlock):
 
 
 class PreNormBlock(_NormedBlock):
+    """``pre_ffn_norm`` may be None for a layer whose feed-forward is of kind "none": the second line is then left out."""
     NORMS = ("pre_mixer_norm", "pre_ffn_norm")
+
+    def __init__(self, params, prefix, rt, mixer, feed_forward):
+        Block.__init__(self, params, prefix, rt, mixer, feed_forward)
+        self.has_ffn = not getattr(feed_forward, "absent", False)
+        if self.has_ffn and not params.get("pre_ffn_norm"):
+            raise ValueError("pre_norm: a layer with a feed-forward needs 'pre_ffn_norm'")
+        self.norms = {n: build_part("norm", params[n], prefix, rt) for n in self.NORMS
+                      if n == "pre_mixer_norm" or self.has_ffn}
 
     def forward(self, stream, ctx, cache) -> None:
         dt = self.rt.dtype
         x = stream.normed(self.norms["pre_mixer_norm"], dt)
         stream.add(self.mixer.forward(x, ctx, cache))
-        x = stream.normed(self.norms["pre_ffn_norm"], dt)
-        stream.add(self.feed_forward.forward(x, ctx))
+        if self.has_ffn:
+            x = stream.normed(self.norms["pre_ffn_norm"], dt)
+            stream.add(self.feed_forward.forward(x, ctx))
 
 
 class PostNormBlock(_NormedBlock):

@@ -1,0 +1,103 @@
+"""A feed-forward made of experts behind a router, with an optional gated shared expert.
+
+``experts`` small gated feed-forwards ``down_e(act(gate_e x) * up_e x)`` without biases; each token uses ``top``
+of them.  The router (all of it 32-bit): logits ``z = R x``, scores ``s = sigmoid(z)``; *choice scores* are
+``s + correction``; the experts form ``groups`` equal groups of neighbours, a group's score is the sum of its
+``group_score_of`` largest choice scores, and only experts of the ``keep_groups`` best groups can be chosen (the
+others' choice scores count as minus infinity); the ``top`` largest choice scores win; the winners' weights are
+their ``s`` (without the correction) divided by their sum plus ``weight_eps``.  The output is the weighted sum
+of the winners' outputs, plus, if there is a shared expert, ``sigmoid(g . x)`` times its output for every token.
+
+Parameters (none is fixed in code): ``hidden_size``, ``experts``, ``top``, ``intermediate_size``, ``activation``
+("silu"), ``score`` ("sigmoid"), ``groups``, ``keep_groups``, ``group_score_of``, ``weight_eps``, the tensor names
+``router``, ``correction`` (None: no correction), ``expert`` (a pattern with ``{}`` for the expert's number) with
+``gate``, ``up``, ``down`` below it, and ``shared``: None or ``{"intermediate_size", "gate", "up", "down",
+"token_gate"}`` (``token_gate`` None: the shared expert is added as it is).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..csrc import ops
+from ..weights.loader import TensorSpec
+from .base import FeedForward, register_part
+from .feed_forward import GatedMLP
+from .linear import kernel_files as linear_kernels
+
+
+class RoutedExperts(FeedForward):
+    graph_safe = True          # the routing stays on the device: no launch depends on which experts were chosen
+
+    def __init__(self, params, prefix, rt):
+        super().__init__(params, prefix, rt)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.E = int(p["experts"])
+        self.top = int(p["top"])
+        self.ff = int(p["intermediate_size"])
+        self.groups = int(p.get("groups") or 1)
+        self.keep = int(p.get("keep_groups") or self.groups)
+        self.group_top = int(p.get("group_score_of") or 1)
+        self.weight_eps = float(p.get("weight_eps") or 0.0)
+        if p.get("activation", "silu") != "silu" or p.get("score", "sigmoid") != "sigmoid":
+            raise ValueError("routed_experts: the kernels know the silu activation and sigmoid scores")
+        if not (1 <= self.top <= self.E) or self.E % self.groups or not (1 <= self.keep <= self.groups) \
+                or self.keep * (self.E // self.groups) < self.top:
+            raise ValueError(f"routed_experts: experts={self.E} top={self.top} groups={self.groups} keep={self.keep}")
+        self.shared: Optional[GatedMLP] = None
+        self.shared_gate_name = None
+        sh = p.get("shared")
+        if sh:
+            self.shared = GatedMLP({"hidden_size": self.hidden, "intermediate_size": int(sh["intermediate_size"]),
+                                    "activation": "silu", "gate": sh["gate"], "up": sh["up"], "down": sh["down"]}, prefix, rt)
+            self.shared_gate_name = sh.get("token_gate")
+
+    def _expert(self, e: int, key: str) -> str:
+        return self.prefix + self.params["expert"].format(e) + self.params[key]
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        specs = {self._name("router"): TensorSpec((self.E, self.hidden))}
+        if self.params.get("correction"):
+            specs[self._name("correction")] = TensorSpec((self.E,), "norm")
+        for e in range(self.E):
+            specs[self._expert(e, "gate")] = TensorSpec((self.ff, self.hidden))
+            specs[self._expert(e, "up")] = TensorSpec((self.ff, self.hidden))
+            specs[self._expert(e, "down")] = TensorSpec((self.hidden, self.ff))
+        if self.shared is not None:
+            specs.update(self.shared.tensor_specs())
+            if self.shared_gate_name:
+                specs[self.prefix + self.shared_gate_name] = TensorSpec((1, self.hidden))
+        return specs
+
+    def bind(self, tensors) -> None:
+        self.w_router = tensors[self._name("router")]
+        self.correction = tensors[self._name("correction")].float().contiguous() if self.params.get("correction") else None
+        dt = tensors[self._expert(0, "gate")].dtype
+        self.w_gate = torch.stack([tensors[self._expert(e, "gate")].to(dt) for e in range(self.E)]).contiguous()
+        self.w_up = torch.stack([tensors[self._expert(e, "up")].to(dt) for e in range(self.E)]).contiguous()
+        self.w_down = torch.stack([tensors[self._expert(e, "down")].to(dt) for e in range(self.E)]).contiguous()
+        self.w_shared_gate = None
+        if self.shared is not None:
+            self.shared.bind(tensors)
+            if self.shared_gate_name:
+                self.w_shared_gate = tensors[self.prefix + self.shared_gate_name].to(self.w_router.dtype).reshape(-1).contiguous()
+
+    def kernel_files(self):
+        return linear_kernels(self.rt.dtype) + ("moe", "activation")
+
+    def forward(self, x, ctx):
+        idx, weight, gate = ops.moe_route(x, self.w_router, self.correction, self.w_shared_gate, self.top, self.groups,
+                                          self.keep, self.group_top, self.weight_eps)
+        shared = None
+        if self.shared is not None:
+            shared = self.shared.forward(x, ctx)              # float32 partial sums [splits, T, hidden]
+            if gate is None:
+                gate = ctx.memo.get("ones")
+                if gate is None or gate.numel() < x.shape[0]:
+                    gate = ctx.memo["ones"] = torch.ones(x.shape[0], dtype=torch.float32, device=x.device)
+        return ops.moe_experts(x, self.w_gate, self.w_up, self.w_down, idx, weight, shared, gate)
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -51,4 +51,37 @@ class RMSNorm(Norm):
         return ops.fold_rmsnorm(h, a if a.dim() == 3 else a.contiguous(), self.weight, self.eps, self.offset, alpha, out_dtype)
 
 
+class LayerNorm(Norm):
+    """``y = (x - mean) / sqrt(var + eps) * w + b`` with the variance as the mean of the squared deviations;
+    statistics, scale and shift in 32-bit.  Parameters: ``size``, ``eps`` and the tensor names ``weight`` and
+    ``bias``.  :meth:`add_apply` is the fused form ``h += a; y = norm(h)`` that an arrangement with unnormed branch
+    outputs reads the stream through."""
+
+    def __init__(self, params, prefix, rt):
+        super().__init__(params, prefix, rt)
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self._name("weight"): TensorSpec((self.size,), "gain"), self._name("bias"): TensorSpec((self.size,), "norm")}
+
+    def bind(self, tensors) -> None:
+        # two short vectors that enter 32-bit arithmetic: kept in 32 bits (exact for what a file stores in 16)
+        self.weight = tensors[self._name("weight")].float().contiguous()
+        self.bias = tensors[self._name("bias")].float().contiguous()
+
+    def kernel_files(self):
+        return ("layernorm", "norm")
+
+    def apply(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        return ops.add_layernorm(x, None, self.weight, self.bias, self.eps, out_dtype)
+
+    def add_apply(self, h: torch.Tensor, a: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """``h += a`` in place (``a`` a branch output or its split-K partial sums), returns ``norm(h)``."""
+        return ops.add_layernorm(h, a, self.weight, self.bias, self.eps, out_dtype)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)

@@ -50,6 +50,8 @@ class ResidualStream:
             self._pending = None
             if post is not None:
                 return post.add_to(self.h, a, norm, out_dtype)
+            if hasattr(norm, "add_apply"):
+                return norm.add_apply(self.h, a, out_dtype)      # the sum and the norm in one kernel
             ops.residual_add(self.h, a)
         self._flush()
         return norm.apply(self.h, out_dtype)
@@ -65,6 +67,11 @@ class ResidualStream:
             return self.h if want is None else out
         self._flush()
         return self.h if want is None else ops.cast(self.h, want)
+
+    def add_rows(self, rows: Optional[torch.Tensor], vector: Optional[torch.Tensor]) -> None:
+        """h += rows (a float32 matrix of the stream's shape) + vector (one float32 row, added to every token)."""
+        self._flush()
+        ops.add_rows(self.h, rows, vector)
 
     def value(self) -> torch.Tensor:
         self._flush()

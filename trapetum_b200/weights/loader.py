@@ -61,7 +61,7 @@ class TensorSpec:
     role: ``"matrix"`` and ``"embedding"`` are drawn N(0, std) in random mode,
     ``"norm"`` N(0, norm_std), ``"gain"`` 1 + N(0, norm_std); ``"table"`` is an integer table (zeros in random
     mode).  ``optional`` tensors may be absent (the part then falls back, for
-    instance a tied output head)."""
+    instance a tied output head).  A size of -1 in ``shape`` is left to the file."""
     shape: Tuple[int, ...]
     role: str = "matrix"
     optional: bool = False
@@ -99,7 +99,8 @@ def load_tensors(folder: str, wanted: Dict[str, TensorSpec], engine_dtype: torch
                 missing.append(name)
             continue
         got = files[name].shape(name)
-        if tuple(got) != tuple(spec.shape):
+        # a size of -1 is the file's to decide (a low rank, for instance); the part checks it when it is bound
+        if len(got) != len(spec.shape) or any(w >= 0 and int(g) != w for g, w in zip(got, spec.shape)):
             wrong_shape.append((name, got, spec.shape))
         stored = files[name].dtype(name)
         if spec.role == "table" and _is_float(stored):
@@ -140,6 +141,9 @@ def random_tensors(wanted: Dict[str, TensorSpec], seed: int, std: float, norm_st
     for name, spec in wanted.items():
         if spec.optional:
             continue
+        if any(n < 0 for n in spec.shape):
+            raise ValueError(f"tensor '{name}' has a size that only a weight file decides ({list(spec.shape)}); "
+                             "random weights need that size in the configuration")
         if spec.role == "table":
             yield name, torch.zeros(spec.shape, dtype=torch.int32, device=device)
             continue
