@@ -21,6 +21,15 @@ def f64(t: torch.Tensor) -> torch.Tensor:
     return t.to(F)
 
 
+def same(x):
+    return x
+
+
+def to_bf16(x: torch.Tensor) -> torch.Tensor:
+    """What a 16-bit engine stores: the value rounded to bfloat16 (used only to size the tests' tolerances)."""
+    return x.to(torch.bfloat16).to(F)
+
+
 def layer_norm(x, w, b, eps):
     mu = x.mean(-1, keepdim=True)
     var = ((x - mu) ** 2).mean(-1, keepdim=True)
@@ -39,17 +48,17 @@ def silu(z):
     return z * torch.sigmoid(z)
 
 
-def gated(h, gate, up, down, act):
-    return (act(h @ gate.T) * (h @ up.T)) @ down.T
+def gated(h, gate, up, down, act, rnd=same):
+    return rnd(act(h @ gate.T) * (h @ up.T)) @ down.T
 
 
-def gla(h, m: dict, t: Dict[str, torch.Tensor], p: str, eps: float, state: Optional[torch.Tensor] = None):
+def gla(h, m: dict, t: Dict[str, torch.Tensor], p: str, eps: float, state: Optional[torch.Tensor] = None, rnd=same):
     """Gated linear attention over one sequence.  ``state`` [heads, dim, vdim] is carried in and returned."""
     H, D, V, tau = m["heads"], m["dim"], m["vdim"], float(m["tau"])
     T = h.shape[0]
-    q = (h @ t[p + "q"].T).view(T, H, D) * D ** -0.5
-    k = (h @ t[p + "k"].T).view(T, H, D)
-    v = (h @ t[p + "v"].T).view(T, H, V)
+    q = rnd(h @ t[p + "q"].T).view(T, H, D) * D ** -0.5
+    k = rnd(h @ t[p + "k"].T).view(T, H, D)
+    v = rnd(h @ t[p + "v"].T).view(T, H, V)
     z = (h @ t[p + "a1"].T) @ t[p + "a2"].T + t[p + "a2.b"]
     alpha = torch.sigmoid(z).pow(1.0 / tau).view(T, H, D)
     S = torch.zeros(H, D, V, dtype=F) if state is None else state.clone()
@@ -58,7 +67,7 @@ def gla(h, m: dict, t: Dict[str, torch.Tensor], p: str, eps: float, state: Optio
         S = alpha[i][:, :, None] * S + k[i][:, :, None] * v[i][:, None, :]
         o[i] = torch.einsum("hdv,hd->hv", S, q[i])
     o = rms_norm(o, t[p + "norm"], eps).reshape(T, H * V)
-    return (o * silu(h @ t[p + "g"].T)) @ t[p + "o"].T, S
+    return rnd(o * silu(rnd(h @ t[p + "g"].T))) @ t[p + "o"].T, S
 
 
 def rotate_half(x, pos, dims: int, base: float):
@@ -72,21 +81,21 @@ def rotate_half(x, pos, dims: int, base: float):
     return torch.cat([u * c - w * s, w * c + u * s, x[..., dims:]], dim=-1)
 
 
-def latent_attention(h, m: dict, t: Dict[str, torch.Tensor], p: str, eps: float, first_pos: int = 0, past=None):
+def latent_attention(h, m: dict, t: Dict[str, torch.Tensor], p: str, eps: float, first_pos: int = 0, past=None, rnd=same):
     """Latent attention over one sequence.  ``past`` = (latents, rotated key parts) of earlier tokens."""
     H, D, R, V, C = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     T = h.shape[0]
     pos = torch.arange(first_pos, first_pos + T)
     q = (h @ t[p + "q"].T).view(T, H, D + R)
-    q_plain, q_rot = q[..., :D], rotate_half(q[..., D:], pos, m["rot"]["dims"], float(m["rot"]["base"]))
+    q_plain, q_rot = rnd(q[..., :D]), rnd(rotate_half(q[..., D:], pos, m["rot"]["dims"], float(m["rot"]["base"])))
     d = h @ t[p + "dkv"].T
-    c = rms_norm(d[:, :C], t[p + "dkv.norm"], eps)
-    k_rot = rotate_half(d[:, C:], pos, m["rot"]["dims"], float(m["rot"]["base"]))
+    c = rnd(rms_norm(d[:, :C], t[p + "dkv.norm"], eps))
+    k_rot = rnd(rotate_half(d[:, C:], pos, m["rot"]["dims"], float(m["rot"]["base"])))
     if past is not None:
         c, k_rot = torch.cat([past[0], c]), torch.cat([past[1], k_rot])
     n = c.shape[0]
-    k_plain = (c @ t[p + "uk"].T).view(n, H, D)
-    v = (c @ t[p + "uv"].T).view(n, H, V)
+    k_plain = rnd(c @ t[p + "uk"].T).view(n, H, D)
+    v = rnd(c @ t[p + "uv"].T).view(n, H, V)
     s = (torch.einsum("thd,nhd->htn", q_plain, k_plain) + torch.einsum("thr,nr->htn", q_rot, k_rot)) * float(m["scale"])
     qpos = pos[:, None]
     kpos = torch.arange(n)[None, :]
@@ -95,7 +104,7 @@ def latent_attention(h, m: dict, t: Dict[str, torch.Tensor], p: str, eps: float,
     mx = torch.maximum(s.max(-1).values, sink[:, None].expand(H, T))
     e = torch.exp(s - mx[..., None])
     w = e / (e.sum(-1) + torch.exp(sink[:, None] - mx))[..., None]
-    o = torch.einsum("htn,nhv->thv", w, v).reshape(T, H * V)
+    o = rnd(torch.einsum("htn,nhv->thv", w, v).reshape(T, H * V))
     return o @ t[p + "o"].T, (c, k_rot)
 
 
@@ -117,16 +126,16 @@ def route(h, r: dict, t: Dict[str, torch.Tensor], p: str):
     return idx, w / (w.sum(-1, keepdim=True) + 1e-20)
 
 
-def moe(h, mlp: dict, t: Dict[str, torch.Tensor], p: str):
+def moe(h, mlp: dict, t: Dict[str, torch.Tensor], p: str, rnd=same):
     idx, w = route(h, mlp["router"], t, p)
     out = torch.zeros(h.shape[0], t[p + "e0.down"].shape[0], dtype=F)
     for i in range(h.shape[0]):
         for j, e in enumerate(idx[i].tolist()):
             q = f"{p}e{e}."
-            out[i] += w[i, j] * gated(h[i:i + 1], t[q + "gate"], t[q + "up"], t[q + "down"], silu)[0]
+            out[i] += w[i, j] * gated(h[i:i + 1], t[q + "gate"], t[q + "up"], t[q + "down"], silu, rnd)[0]
     if mlp.get("shared"):
         q = p + "shared."
-        out = out + torch.sigmoid(h @ t[q + "sg"].T) * gated(h, t[q + "gate"], t[q + "up"], t[q + "down"], silu)
+        out = out + torch.sigmoid(h @ t[q + "sg"].T) * gated(h, t[q + "gate"], t[q + "up"], t[q + "down"], silu, rnd)
     return out
 
 
@@ -146,8 +155,9 @@ def schedule(cfg: dict) -> List[tuple]:
 class Plain:
     """One sequence, fed in pieces: ``feed(tokens)`` returns (logits of these tokens, stream after every layer run)."""
 
-    def __init__(self, cfg: dict, tensors: Dict[str, torch.Tensor]):
+    def __init__(self, cfg: dict, tensors: Dict[str, torch.Tensor], rnd=same):
         self.cfg = cfg
+        self.rnd = rnd
         self.t = {k: f64(v) for k, v in tensors.items()}
         self.runs = schedule(cfg)
         self.memory = [None] * len(self.runs)
@@ -166,25 +176,57 @@ class Plain:
                     x = x + x0
                 x = x + t["loop.step"][rep]
             p = f"l{i}."
-            h = layer_norm(x, t[p + "norm1"], t[p + "norm1.b"], eps)
+            rnd = self.rnd
+            h = rnd(layer_norm(x, t[p + "norm1"], t[p + "norm1.b"], eps))
             if L["type"] == "gla":
-                y, self.memory[r] = gla(h, L["mixer"], t, p + "mix.", eps, self.memory[r])
+                y, self.memory[r] = gla(h, L["mixer"], t, p + "mix.", eps, self.memory[r], rnd)
             elif L["type"] == "latent_attention":
-                y, self.memory[r] = latent_attention(h, L["mixer"], t, p + "mix.", eps, self.n, self.memory[r])
+                y, self.memory[r] = latent_attention(h, L["mixer"], t, p + "mix.", eps, self.n, self.memory[r], rnd)
             else:
                 raise ValueError(L["type"])
             x = x + y
             if L.get("mlp"):
-                h = layer_norm(x, t[p + "norm2"], t[p + "norm2.b"], eps)
+                h = rnd(layer_norm(x, t[p + "norm2"], t[p + "norm2.b"], eps))
                 if L["mlp"]["kind"] == "dense":
-                    y = gated(h, t[p + "mlp.gate"], t[p + "mlp.up"], t[p + "mlp.down"], gelu_tanh)
+                    y = gated(h, t[p + "mlp.gate"], t[p + "mlp.up"], t[p + "mlp.down"], gelu_tanh, rnd)
                 else:
-                    y = moe(h, L["mlp"], t, p + "mlp.")
+                    y = moe(h, L["mlp"], t, p + "mlp.", rnd)
                 x = x + y
             after.append(x.clone())
         self.n += len(tokens)
-        z = layer_norm(x, t["final.norm"], t["final.norm.b"], eps) @ t["head"].T
+        z = self.rnd(layer_norm(x, t["final.norm"], t["final.norm.b"], eps)) @ t["head"].T
         cap = cfg.get("logit_softcap")
         if cap:
             z = float(cap) * torch.tanh(z / float(cap))
         return z, torch.stack(after)
+
+
+def forward(cfg: dict, tensors, ids, rnd=same) -> torch.Tensor:
+    """Logits of a whole sequence, [tokens, vocab]."""
+    return Plain(cfg, tensors, rnd).feed(list(ids))[0]
+
+
+def forward_stepwise(cfg: dict, tensors, ids, first: int = 1) -> torch.Tensor:
+    """The same logits, from ``first`` tokens at once and then one token at a time."""
+    m = Plain(cfg, tensors)
+    out = [m.feed(list(ids[:first]))[0]] + [m.feed([t])[0] for t in ids[first:]]
+    return torch.cat(out)
+
+
+def generate_greedy(cfg: dict, tensors, prompt, n_new: int) -> List[int]:
+    m = Plain(cfg, tensors)
+    z = m.feed(list(prompt))[0]
+    out = []
+    for _ in range(n_new):
+        out.append(int(z[-1].argmax()))
+        z = m.feed([out[-1]])[0]
+    return out
+
+
+def load_folder(folder: str):
+    import json
+    import os
+    from safetensors.torch import load_file
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    return cfg, {k: f64(v) for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
