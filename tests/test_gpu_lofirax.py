@@ -86,9 +86,10 @@ def test_layer_norm_with_the_sum_before_it(rows, width, splits, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H, D, V, rank, lens", [(3, 8, 16, 4, [19, 1, 8]), (1, 20, 40, 5, [33]), (2, 64, 70, 16, [9, 70]),
-                                                 (2, 130, 32, 3, [12, 5])])
+                                                 (2, 130, 32, 3, [12, 5]), (1, 16, 32, 2, [300, 64, 129])])
 def test_gated_linear_attention_between_its_products(H, D, V, rank, lens, dtype):
-    """Whole sequences in one call, then the same sequences continued from the states the first call left."""
+    """Whole sequences in one call, then the same sequences continued from the states the first call left.  The
+    longest case is cut into chunks in time (a chunk's edge at 64 and at 128: one sequence ends on it, one just after)."""
     from trapetum_b200.csrc import ops
     dt = DTYPES[dtype]
     g = torch.Generator().manual_seed(D * V)
@@ -112,7 +113,8 @@ def test_gated_linear_attention_between_its_products(H, D, V, rank, lens, dtype)
         starts = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
         tok_seq = torch.repeat_interleave(torch.arange(B), torch.tensor(lens)).int()
         out = ops.gla(dev(proj, dt), dev(low3, torch.float32), dev(t["a2"], torch.float32), dev(t["a2.b"], torch.float32), tau,
-                      D ** -0.5, dev(t["norm"], torch.float32), eps, H, D, V, state, dev(starts), dev(tok_seq), dev(slots), B)
+                      D ** -0.5, dev(t["norm"], torch.float32), eps, H, D, V, state, dev(starts), dev(tok_seq), dev(slots), B,
+                      max_seq_len=max(lens))
         for b in range(B):
             # the oracle gets what the kernel gets: products rounded to the activations' dtype
             rnd = plain.to_bf16 if dtype == "bfloat16" else plain.same
@@ -213,11 +215,13 @@ def test_router_choices_and_weights(E, top, groups, keep):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_experts_weighted_sum_with_a_shared_expert(dtype):
+@pytest.mark.parametrize("T, W, E, ff, top", [(21, 72, 5, 24, 2), (150, 72, 5, 24, 2), (333, 128, 16, 200, 3), (70, 40, 3, 8, 3)])
+def test_experts_weighted_sum_with_a_shared_expert(T, W, E, ff, top, dtype):
+    """Few pairs run one by one, many (in bfloat16) grouped by expert on the tensor cores: tiles that are not full,
+    experts that nobody chose, widths that are no multiples of the tile."""
     from trapetum_b200.csrc import ops
     dt = DTYPES[dtype]
     g = torch.Generator().manual_seed(8)
-    T, W, E, ff, top = 21, 72, 5, 24, 2
     x = torch.randn(T, W, generator=g).to(dt)
     gw, uw, dw = (torch.randn(E, a, b, generator=g).to(dt) / 5 for a, b in ((ff, W), (ff, W), (W, ff)))
     idx = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).int()
@@ -388,7 +392,8 @@ def test_a_slow_state_is_carried_through_long_decoding(tmp_path, dtype):
     ids = prompts(40, [300], seed=8)[0]
     truth = plain.forward(cfg, wd, ids)
     other = [(t + 1) % 40 for t in ids[:5]] + ids[5:]
-    assert float(position_errors(plain.forward(cfg, wd, other)[-1:], truth[-1:])) > 0.02
+    # five of three hundred tokens: a small share of the state, but two hundred times the 32-bit tolerance
+    assert float(position_errors(plain.forward(cfg, wd, other)[-1:], truth[-1:])) > 0.005
     eng = tb.Engine(tb.load_model(folder, dtype, DEV), max_tokens=512)
     s = eng.start(1)
     got = [eng.step(s, [ids[:10]], [[9]])] + [eng.step(s, [[t]], [[0]]).clone() for t in ids[10:]]

@@ -35,6 +35,10 @@ struct GlaArgs {
     float* y;                                         // [T][H*V] scratch
     void* out;                                        // [T][H*V]
     int heads, D, V, batch, n_tokens;
+    // long prompts cut into chunks in time that run side by side (0 chunks: one CTA walks a whole sequence)
+    float* chunk_state;                               // [batch][n_chunks][H*D*V]: a chunk's end state from zero, then its start state
+    float* chunk_decay;                               // [batch][n_chunks][H*D]: the product of the chunk's decays
+    int chunk_len, n_chunks;
 };
 
 __global__ void gla_decay_kernel(GlaArgs a) {
@@ -63,7 +67,10 @@ __global__ void gla_decay_kernel(GlaArgs a) {
 constexpr int GLA_TT = 8;          // tokens per tile
 constexpr int GLA_WARPS = 8;       // slices of the key channels
 
-template <typename T, int DPT>
+// MODE 0: a sequence from the state its slot holds to the state it leaves there, with outputs.
+// MODE 1: a chunk from a zero state, without outputs: its end state and the product of its decays (for the fold).
+// MODE 2: a chunk from the start state the fold left, with outputs; the last chunk leaves the sequence's state.
+template <typename T, int DPT, int MODE>
 __global__ void __launch_bounds__(GLA_WARPS * 32) gla_scan_kernel(GlaArgs a) {
     pdl_launch_dependents();
     constexpr int DP = DPT * GLA_WARPS;                // key channels, padded
@@ -71,18 +78,25 @@ __global__ void __launch_bounds__(GLA_WARPS * 32) gla_scan_kernel(GlaArgs a) {
     __shared__ float v_s[GLA_TT][32];
     __shared__ float part_s[GLA_TT][GLA_WARPS][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int h = blockIdx.y, b = blockIdx.z;
+    const int h = blockIdx.y;
+    const int b = MODE == 0 ? blockIdx.z : blockIdx.z / a.n_chunks;
+    const int chunk = MODE == 0 ? 0 : blockIdx.z % a.n_chunks;
     const int D = a.D, V = a.V, HD = a.heads * D, HV = a.heads * V;
     const int v0 = blockIdx.x * 32, vch = v0 + lane;
     const bool v_ok = vch < V;
     pdl_wait();
-    const int s0 = a.seq_start[b], s1 = a.seq_start[b + 1];
+    int s0 = a.seq_start[b], s1 = a.seq_start[b + 1];
+    const int seq_end = s1;
+    if (MODE != 0) { s0 = min(s1, s0 + chunk * a.chunk_len); s1 = min(s1, s0 + a.chunk_len); }
     float* st = a.state + (size_t)a.slot_ids[b] * a.state_stride + (size_t)h * D * V;
-    float S[DPT];
+    float* cst = MODE == 0 ? nullptr : a.chunk_state + ((size_t)b * a.n_chunks + chunk) * a.heads * D * V + (size_t)h * D * V;
+    float S[DPT], P[DPT];
 #pragma unroll
     for (int j = 0; j < DPT; j++) {
         const int d = warp * DPT + j;
-        S[j] = (d < D && v_ok) ? st[(size_t)d * V + vch] : 0.f;
+        const float* from = MODE == 2 ? cst : st;
+        S[j] = (MODE != 1 && d < D && v_ok) ? from[(size_t)d * V + vch] : 0.f;
+        P[j] = 1.f;
     }
     const T* proj = (const T*)a.proj;
     for (int t0 = s0; t0 < s1; t0 += GLA_TT) {
@@ -110,12 +124,13 @@ __global__ void __launch_bounds__(GLA_WARPS * 32) gla_scan_kernel(GlaArgs a) {
             for (int j = 0; j < DPT; j++) {
                 const int d = warp * DPT + j;
                 S[j] = fmaf(d_s[tt][d], S[j], k_s[tt][d] * vv);
-                acc = fmaf(S[j], q_s[tt][d], acc);
+                if (MODE == 1) P[j] *= d_s[tt][d];
+                else acc = fmaf(S[j], q_s[tt][d], acc);
             }
-            part_s[tt][warp][lane] = acc;
+            if (MODE != 1) part_s[tt][warp][lane] = acc;
         }
         __syncthreads();
-        {
+        if (MODE != 1) {
             const int tt = warp;
             if (tt < nt && v_ok) {
                 float o = 0.f;
@@ -127,10 +142,36 @@ __global__ void __launch_bounds__(GLA_WARPS * 32) gla_scan_kernel(GlaArgs a) {
         // the next tile's staging writes q_s..v_s, which nobody reads any more; part_s is written again only
         // after the next barrier
     }
+    if (MODE == 2 && s1 != seq_end) return;            // only the chunk that holds the sequence's end leaves its state
+    if (MODE == 2 && s0 == s1 && chunk != 0) return;   // (an empty chunk after the end: the one before it did)
 #pragma unroll
     for (int j = 0; j < DPT; j++) {
         const int d = warp * DPT + j;
-        if (d < D && v_ok) st[(size_t)d * V + vch] = S[j];
+        float* to = MODE == 1 ? cst : st;
+        if (d < D && v_ok) to[(size_t)d * V + vch] = S[j];
+        if (MODE == 1 && d < D && blockIdx.x == 0 && lane == 0)
+            a.chunk_decay[((size_t)b * a.n_chunks + chunk) * a.heads * D + (size_t)h * D + d] = P[j];
+    }
+}
+
+// Start states of the chunks from their end states: S_start[0] = the slot's state, S_start[c+1] = P_c S_start[c] + E_c,
+// element by element; chunk_state[c] is turned from E_c into S_start[c] in place.
+__global__ void gla_fold_kernel(GlaArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int D = a.D, V = a.V;
+    const long long per = (long long)a.heads * D * V;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= per * a.batch) return;
+    const int b = (int)(i / per);
+    const long long e = i % per;                      // (h, d, v)
+    const long long hd = e / V;                       // h * D + d
+    float S = a.state[(size_t)a.slot_ids[b] * a.state_stride + e];
+    for (int c = 0; c < a.n_chunks; c++) {
+        float* cs = a.chunk_state + ((size_t)b * a.n_chunks + c) * per + e;
+        const float E = *cs;
+        *cs = S;
+        S = fmaf(a.chunk_decay[((size_t)b * a.n_chunks + c) * a.heads * D + hd], S, E);
     }
 }
 
@@ -176,17 +217,44 @@ extern "C" int tb_gla_scan(const GlaArgs* args, int dtype, cudaStream_t stream) 
     const GlaArgs& a = *args;
     int dpt = 1;
     while (dpt * GLA_WARPS < a.D) dpt <<= 1;
-    dim3 grid((a.V + 31) / 32, a.heads, a.batch);
-#define GLA_SCAN(N) TB_DISPATCH_1(dtype, T, tb_launch(gla_scan_kernel<T, N>, dim3(grid), dim3(GLA_WARPS * 32), 0, stream, a))
-    switch (dpt) {
-    case 1: GLA_SCAN(1); break;
-    case 2: GLA_SCAN(2); break;
-    case 4: GLA_SCAN(4); break;
-    case 8: GLA_SCAN(8); break;
-    case 16: GLA_SCAN(16); break;
-    default: GLA_SCAN(32); break;
+    const bool chunks = a.n_chunks > 1;
+    if (chunks && (a.chunk_len <= 0 || a.chunk_state == nullptr || a.chunk_decay == nullptr || (long long)a.batch * a.n_chunks > 65535))
+        return tb_refuse("gla: %d chunks of %d tokens need their scratch (and batch x chunks <= 65535)", a.n_chunks, a.chunk_len);
+    dim3 grid((a.V + 31) / 32, a.heads, chunks ? a.batch * a.n_chunks : a.batch);
+#define GLA_SCAN_M(N, M) TB_DISPATCH_1(dtype, T, tb_launch(gla_scan_kernel<T, N, M>, dim3(grid), dim3(GLA_WARPS * 32), 0, stream, a))
+#define GLA_SCAN(N) do { if (mode == 0) GLA_SCAN_M(N, 0); else if (mode == 1) GLA_SCAN_M(N, 1); else GLA_SCAN_M(N, 2); } while (0)
+    for (int pass = 0; pass < (chunks ? 3 : 1); pass++) {
+        if (chunks && pass == 1) {
+            const long long n = (long long)a.batch * a.heads * a.D * a.V;
+            tb_launch(gla_fold_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, a);
+        } else {
+            const int mode = chunks ? (pass == 0 ? 1 : 2) : 0;
+            switch (dpt) {
+            case 1: GLA_SCAN(1); break;
+            case 2: GLA_SCAN(2); break;
+            case 4: GLA_SCAN(4); break;
+            case 8: GLA_SCAN(8); break;
+            case 16: GLA_SCAN(16); break;
+            default: GLA_SCAN(32); break;
+            }
+        }
+        const int st = tb_launch_status();
+        if (st) return st;
     }
-    return tb_launch_status();
+    return 0;
+}
+
+// How a step of whole prompts is cut in time: chunks of at least 64 tokens, as many as give every SM about two CTAs.
+extern "C" int tb_gla_plan(int heads, int V, int batch, int max_seq_len, int sms, int* chunk_len) {
+    const long long ctas = (long long)((V + 31) / 32) * heads * batch;
+    int want = (int)((2LL * sms + ctas - 1) / ctas);
+    int most = max_seq_len / 64;
+    if (want > most) want = most;
+    if (want <= 1) { *chunk_len = 0; return 1; }
+    int len = (max_seq_len + want - 1) / want;
+    len = (len + GLA_TT - 1) / GLA_TT * GLA_TT;
+    *chunk_len = len;
+    return (max_seq_len + len - 1) / len;
 }
 
 extern "C" int tb_gla_gate_norm(const GlaArgs* args, int dtype, cudaStream_t stream) {

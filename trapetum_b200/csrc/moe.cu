@@ -177,6 +177,224 @@ __global__ void __launch_bounds__(256) moe_down_kernel(MoeExpertArgs a) {
     }
 }
 
+// ---------------------------------------------------------------------------
+// Many tokens (bfloat16): the (token, expert) pairs are grouped by expert on the device and every expert's
+// pairs go through tensor-core products in tiles of 64 pairs, so that an expert's matrices are read once
+// per tile of pairs and not once per pair.  Nothing here depends on values the host knows: the grid is
+// sized for the most tiles there can be and the surplus CTAs leave at once.
+//
+//   tb_moe_group     counts, offsets and the pair list ordered by expert; the table of tiles
+//   tb_moe_grouped   act = silu(G_e x) * (U_e x) per pair (one launch), pair outputs D_e act times the pair's
+//                    weight in 32-bit (one launch), and their sum per token with the shared expert (one launch)
+// ---------------------------------------------------------------------------
+constexpr int MG_BM = 64, MG_BN = 128, MG_BK = 32, MG_PITCH = MG_BK * 2 + 16;
+
+struct MoeGroupArgs {
+    const int* idx;            // [P] expert of every pair (P = tokens * top)
+    int* perm;                 // [P] pairs ordered by expert
+    int* tile_expert;          // [max_tiles]
+    int* tile_row0;            // [max_tiles] first position in perm
+    int* tile_rows;            // [max_tiles] pairs in the tile
+    int* n_tiles;              // [1]
+    int P, E, max_tiles;
+};
+
+__global__ void __launch_bounds__(1024) moe_group_kernel(MoeGroupArgs a) {
+    pdl_launch_dependents();
+    extern __shared__ int sm[];                       // [E] counts, [E] offsets, [E] cursors, [E] first tile
+    int* cnt = sm; int* off = sm + a.E; int* cur = sm + 2 * a.E; int* tile0 = sm + 3 * a.E;
+    for (int e = threadIdx.x; e < a.E; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
+    __syncthreads();
+    pdl_wait();
+    for (int p = threadIdx.x; p < a.P; p += blockDim.x) atomicAdd(&cnt[a.idx[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int o = 0, t = 0;
+        for (int e = 0; e < a.E; e++) { off[e] = o; tile0[e] = t; o += cnt[e]; t += (cnt[e] + MG_BM - 1) / MG_BM; }
+        *a.n_tiles = t;
+    }
+    __syncthreads();
+    // within an expert the pairs keep no particular order: every pair's result depends on its own row only
+    for (int p = threadIdx.x; p < a.P; p += blockDim.x) {
+        const int e = a.idx[p];
+        a.perm[off[e] + atomicAdd(&cur[e], 1)] = p;
+    }
+    for (int e = threadIdx.x; e < a.E; e += blockDim.x) {
+        const int nt = (cnt[e] + MG_BM - 1) / MG_BM;
+        for (int i = 0; i < nt; i++) {
+            const int t = tile0[e] + i;
+            if (t < a.max_tiles) {
+                a.tile_expert[t] = e; a.tile_row0[t] = off[e] + i * MG_BM;
+                a.tile_rows[t] = min(MG_BM, cnt[e] - i * MG_BM);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ uint32_t mg_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mg_cp16(void* dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;                     // 0 source bytes: the 16 destination bytes become zero
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(mg_smem(dst)), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void mg_ldsm(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mg_mma(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+struct MoeGroupedArgs {
+    const bf16* x; long long x_stride;                // [T][W]
+    const bf16* gate_w; const bf16* up_w;             // [E][ff][W]
+    const bf16* down_w;                               // [E][W][ff]
+    const int* perm; const int* tile_expert; const int* tile_row0; const int* tile_rows; const int* n_tiles;
+    const float* weight;                              // [P]
+    bf16* act;                                        // [P][ff]
+    float* pair_out;                                  // [P][W]
+    int W, ff, top;
+};
+
+// GATED: rows of x (by pair / top) times [G_e ; U_e] for 64 columns of ff, then silu(g) * u  ->  act[pair]
+// else:  rows of act (by pair) times D_e for 128 columns of W, times the pair's weight          ->  pair_out[pair]
+template <bool GATED>
+__global__ void __launch_bounds__(128) moe_grouped_kernel(MoeGroupedArgs a) {
+    pdl_launch_dependents();
+    __shared__ __align__(16) unsigned char smem[2 * (MG_BM + MG_BN) * MG_PITCH];
+    __shared__ int row_src[MG_BM];
+    const int tile = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_wait();
+    if (tile >= *a.n_tiles) return;
+    const int e = a.tile_expert[tile], row0 = a.tile_row0[tile], rows = a.tile_rows[tile];
+    const int K = GATED ? a.W : a.ff;
+    const int N = GATED ? a.ff : a.W;
+    const int n0 = blockIdx.y * (GATED ? MG_BN / 2 : MG_BN);
+    if (threadIdx.x < MG_BM) {
+        const int p = threadIdx.x < rows ? a.perm[row0 + threadIdx.x] : -1;
+        row_src[threadIdx.x] = p;
+    }
+    __syncthreads();
+    const bf16* A = GATED ? a.x : a.act;
+    const long long a_stride = GATED ? a.x_stride : a.ff;
+    const bf16* B0 = GATED ? a.gate_w + (size_t)e * a.ff * a.W : a.down_w + (size_t)e * a.W * a.ff;
+    const bf16* B1 = a.up_w + (size_t)e * a.ff * a.W;
+    auto stage_a = [&](int s) { return smem + (size_t)s * (MG_BM + MG_BN) * MG_PITCH; };
+    auto stage_b = [&](int s) { return stage_a(s) + MG_BM * MG_PITCH; };
+    auto load = [&](int s, int k0) {
+        unsigned char* sa = stage_a(s); unsigned char* sb = stage_b(s);
+        for (int c = threadIdx.x; c < MG_BM * 4; c += 128) {
+            const int r = c >> 2, ch = c & 3, k = k0 + ch * 8;
+            const int p = row_src[r];
+            const bool ok = p >= 0 && k < K;
+            const bf16* src = A + (size_t)(ok ? (GATED ? p / a.top : p) : 0) * a_stride + (ok ? k : 0);
+            mg_cp16(sa + r * MG_PITCH + ch * 16, src, ok);
+        }
+        for (int c = threadIdx.x; c < MG_BN * 4; c += 128) {
+            const int r = c >> 2, ch = c & 3, k = k0 + ch * 8;
+            int n; const bf16* base;
+            if (GATED) { n = n0 + (r & 63); base = (r < 64) ? B0 : B1; } else { n = n0 + r; base = B0; }
+            const bool ok = n < N && k < K;
+            mg_cp16(sb + r * MG_PITCH + ch * 16, base + (size_t)(ok ? n : 0) * K + (ok ? k : 0), ok);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float acc[MG_BN / 8][4];
+#pragma unroll
+    for (int n = 0; n < MG_BN / 8; n++) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
+    const int nk = (K + MG_BK - 1) / MG_BK;
+    load(0, 0);
+    for (int kb = 0; kb < nk; kb++) {
+        if (kb + 1 < nk) { load((kb + 1) & 1, (kb + 1) * MG_BK); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        const unsigned char* sa = stage_a(kb & 1); const unsigned char* sb = stage_b(kb & 1);
+#pragma unroll
+        for (int ks = 0; ks < MG_BK / 16; ks++) {
+            uint32_t fa[4];
+            mg_ldsm(mg_smem(sa + (warp * 16 + (lane & 15)) * MG_PITCH + (ks * 16 + (lane >> 4) * 8) * 2), fa[0], fa[1], fa[2], fa[3]);
+#pragma unroll
+            for (int n = 0; n < MG_BN / 8; n += 2) {
+                uint32_t b0, b1, b2, b3;
+                mg_ldsm(mg_smem(sb + (n * 8 + (lane >> 4) * 8 + (lane & 7)) * MG_PITCH + (ks * 16 + ((lane >> 3) & 1) * 8) * 2), b0, b1, b2, b3);
+                mg_mma(acc[n], fa, b0, b1);
+                mg_mma(acc[n + 1], fa, b2, b3);
+            }
+        }
+        __syncthreads();                              // the load after next overwrites this stage
+    }
+    const int ra = warp * 16 + (lane >> 2), rb = ra + 8, cq = (lane & 3) * 2;
+    const int pa = row_src[ra], pb = row_src[rb];
+    if (GATED) {
+#pragma unroll
+        for (int n = 0; n < MG_BN / 16; n++) {
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int col = n0 + n * 8 + cq + j;
+                if (col >= N) continue;
+                const float ga = acc[n][j], ua = acc[n + MG_BN / 16][j], gb = acc[n][2 + j], ub = acc[n + MG_BN / 16][2 + j];
+                if (pa >= 0) a.act[(size_t)pa * a.ff + col] = __float2bfloat16_rn(ga / (1.f + expf(-ga)) * ua);
+                if (pb >= 0) a.act[(size_t)pb * a.ff + col] = __float2bfloat16_rn(gb / (1.f + expf(-gb)) * ub);
+            }
+        }
+    } else {
+        const float wa = pa >= 0 ? a.weight[pa] : 0.f, wb = pb >= 0 ? a.weight[pb] : 0.f;
+#pragma unroll
+        for (int n = 0; n < MG_BN / 8; n++) {
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int col = n0 + n * 8 + cq + j;
+                if (col >= N) continue;
+                if (pa >= 0) a.pair_out[(size_t)pa * a.W + col] = acc[n][j] * wa;
+                if (pb >= 0) a.pair_out[(size_t)pb * a.W + col] = acc[n][2 + j] * wb;
+            }
+        }
+    }
+}
+
+__global__ void moe_sum_pairs_kernel(const float* __restrict__ pair_out, const float* __restrict__ shared, int shared_splits,
+                                     long long shared_split_stride, const float* __restrict__ gate, float* __restrict__ out,
+                                     long long n, int W, int top) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long t = i / W; const int c = (int)(i % W);
+    float acc = 0.f;
+    for (int k = 0; k < top; k++) acc += pair_out[((size_t)t * top + k) * W + c];      // in the order of the choice
+    if (shared != nullptr) {
+        float sh = 0.f;
+        for (int s = 0; s < shared_splits; s++) sh += shared[(size_t)s * shared_split_stride + i];
+        acc = fmaf(gate[t], sh, acc);
+    }
+    out[i] = acc;
+}
+
+extern "C" int tb_moe_group(const MoeGroupArgs* args, cudaStream_t stream) {
+    const MoeGroupArgs& a = *args;
+    if (a.P <= 0) return 0;
+    if (a.E <= 0 || a.E > 2048) return tb_refuse("moe_group: %d experts", a.E);
+    tb_launch(moe_group_kernel, dim3(1), dim3(1024), (size_t)4 * a.E * sizeof(int), stream, a);
+    return tb_launch_status();
+}
+
+extern "C" int tb_moe_grouped(const MoeGroupedArgs* args, const float* shared, int shared_splits, long long shared_split_stride,
+                              const float* gate, float* out, int n_tokens, int max_tiles, cudaStream_t stream) {
+    const MoeGroupedArgs& a = *args;
+    if (n_tokens <= 0) return 0;
+    if (a.W % 8 || a.ff % 8 || ((uintptr_t)a.x & 15) || (a.x_stride % 8))
+        return tb_refuse("moe_grouped: W=%d and ff=%d must be multiples of 8 and the rows 16-byte aligned", a.W, a.ff);
+    tb_launch(moe_grouped_kernel<true>, dim3(max_tiles, (a.ff + 63) / 64), dim3(128), 0, stream, a);
+    int st = tb_launch_status();
+    if (st) return st;
+    tb_launch(moe_grouped_kernel<false>, dim3(max_tiles, (a.W + MG_BN - 1) / MG_BN), dim3(128), 0, stream, a);
+    st = tb_launch_status();
+    if (st) return st;
+    const long long n = (long long)n_tokens * a.W;
+    tb_launch(moe_sum_pairs_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const float*)a.pair_out, shared,
+              shared_splits, shared_split_stride, gate, out, n, a.W, a.top);
+    return tb_launch_status();
+}
+
 extern "C" int tb_moe_route(const MoeRouteArgs* args, int x_dtype, int w_dtype, cudaStream_t stream) {
     const MoeRouteArgs& a = *args;
     if (a.n_tokens <= 0) return 0;

@@ -1154,13 +1154,16 @@ class _GlaArgs(ctypes.Structure):
                 ("norm_w", c_void_p), ("eps", c_float), ("state", c_void_p), ("state_stride", c_longlong),
                 ("seq_start", c_void_p), ("token_seq", c_void_p), ("slot_ids", c_void_p),
                 ("decay", c_void_p), ("y", c_void_p), ("out", c_void_p),
-                ("heads", c_int), ("D", c_int), ("V", c_int), ("batch", c_int), ("n_tokens", c_int)]
+                ("heads", c_int), ("D", c_int), ("V", c_int), ("batch", c_int), ("n_tokens", c_int),
+                ("chunk_state", c_void_p), ("chunk_decay", c_void_p), ("chunk_len", c_int), ("n_chunks", c_int)]
 
 
 def gla(proj: torch.Tensor, low: torch.Tensor, a2: torch.Tensor, a2_bias: torch.Tensor, tau: float, q_scale: float,
         norm_w: torch.Tensor, eps: float, heads: int, key_dim: int, value_dim: int, state: torch.Tensor,
-        seq_start: torch.Tensor, token_seq: torch.Tensor, slot_ids: torch.Tensor, batch: int) -> torch.Tensor:
-    """Gated linear attention between its products (see gla.cu).  ``proj`` [T, 2 H D + 2 H V]: q, k, v and the output
+        seq_start: torch.Tensor, token_seq: torch.Tensor, slot_ids: torch.Tensor, batch: int,
+        max_seq_len: int = 0) -> torch.Tensor:
+    """Gated linear attention between its products (see gla.cu).  ``max_seq_len`` (the longest sequence of a step of
+    whole prompts, 0 if unknown or one token each) lets few long prompts be cut into chunks that run side by side.  ``proj`` [T, 2 H D + 2 H V]: q, k, v and the output
     gate's pre-activation, in the compute dtype; ``low`` float32 [splits, T, rank]: partial sums of the decay's first
     product; ``a2`` float32 [H D, rank], ``a2_bias`` float32 [H D], ``norm_w`` float32 [V]; ``state`` float32
     [slots, H D V], rows picked by ``slot_ids``, read and written.  Returns [T, H V] in the compute dtype."""
@@ -1193,8 +1196,19 @@ def gla(proj: torch.Tensor, low: torch.Tensor, a2: torch.Tensor, a2_bias: torch.
     a.decay = decay.data_ptr(); a.y = y.data_ptr(); a.out = out.data_ptr()
     a.heads = heads; a.D = key_dim; a.V = value_dim; a.batch = batch; a.n_tokens = T
     lib = build.load("gla")
+    scan_launches = 1
+    if max_seq_len > 0:
+        chunk_len = c_int(0)
+        n_chunks = int(lib.tb_gla_plan(c_int(heads), c_int(value_dim), c_int(batch), c_int(int(max_seq_len)),
+                                       c_int(sm_count(proj.device)), ctypes.byref(chunk_len)))
+        if n_chunks > 1 and batch * n_chunks <= 65535:
+            chunk_state = torch.empty((batch, n_chunks, HD * value_dim), dtype=torch.float32, device=proj.device)
+            chunk_decay = torch.empty((batch, n_chunks, HD), dtype=torch.float32, device=proj.device)
+            a.chunk_state = chunk_state.data_ptr(); a.chunk_decay = chunk_decay.data_ptr()
+            a.chunk_len = chunk_len.value; a.n_chunks = n_chunks
+            scan_launches = 3
     _check(lib, lib.tb_gla_decay(ctypes.byref(a), _stream()), "gla_decay")
-    _check(lib, lib.tb_gla_scan(ctypes.byref(a), c_int(code(dt)), _stream()), "gla_scan")
+    _check(lib, lib.tb_gla_scan(ctypes.byref(a), c_int(code(dt)), _stream()), "gla_scan", scan_launches)
     _check(lib, lib.tb_gla_gate_norm(ctypes.byref(a), c_int(code(dt)), _stream()), "gla_gate_norm")
     return out
 
@@ -1361,6 +1375,51 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.
     return idx, weight, gate
 
 
+MOE_GROUPED_FROM = 128      # (token, expert) pairs from which the experts' products run grouped on the tensor cores
+
+
+class _MoeGroupArgs(ctypes.Structure):
+    _fields_ = [("idx", c_void_p), ("perm", c_void_p), ("tile_expert", c_void_p), ("tile_row0", c_void_p),
+                ("tile_rows", c_void_p), ("n_tiles", c_void_p), ("P", c_int), ("E", c_int), ("max_tiles", c_int)]
+
+
+class _MoeGroupedArgs(ctypes.Structure):
+    _fields_ = [("x", c_void_p), ("x_stride", c_longlong), ("gate_w", c_void_p), ("up_w", c_void_p), ("down_w", c_void_p),
+                ("perm", c_void_p), ("tile_expert", c_void_p), ("tile_row0", c_void_p), ("tile_rows", c_void_p),
+                ("n_tiles", c_void_p), ("weight", c_void_p), ("act", c_void_p), ("pair_out", c_void_p),
+                ("W", c_int), ("ff", c_int), ("top", c_int)]
+
+
+def _moe_grouped(x, gate_w, up_w, down_w, idx, weight, shared, gate, out):
+    """The experts' products with the pairs grouped by expert (bfloat16, tensor cores; see moe.cu).  The grid holds the
+    most tiles there can be, so nothing the host does depends on which experts were chosen."""
+    T, W = x.shape
+    E, ff = gate_w.shape[0], gate_w.shape[1]
+    top = idx.shape[1]
+    P = T * top
+    max_tiles = (P + 63) // 64 + min(E, P)
+    ints = torch.empty(P + 3 * max_tiles + 1, dtype=torch.int32, device=x.device)
+    perm, te, tr0, trn, nt = (ints[:P], ints[P:P + max_tiles], ints[P + max_tiles:P + 2 * max_tiles],
+                              ints[P + 2 * max_tiles:P + 3 * max_tiles], ints[P + 3 * max_tiles:])
+    act = torch.empty((P, ff), dtype=x.dtype, device=x.device)
+    pair_out = torch.empty((P, W), dtype=torch.float32, device=x.device)
+    g = _MoeGroupArgs()
+    g.idx = idx.data_ptr(); g.perm = perm.data_ptr(); g.tile_expert = te.data_ptr(); g.tile_row0 = tr0.data_ptr()
+    g.tile_rows = trn.data_ptr(); g.n_tiles = nt.data_ptr(); g.P = P; g.E = E; g.max_tiles = max_tiles
+    lib = build.load("moe")
+    _check(lib, lib.tb_moe_group(ctypes.byref(g), _stream()), "moe_group")
+    a = _MoeGroupedArgs()
+    a.x = x.data_ptr(); a.x_stride = x.stride(0)
+    a.gate_w = gate_w.data_ptr(); a.up_w = up_w.data_ptr(); a.down_w = down_w.data_ptr()
+    a.perm = perm.data_ptr(); a.tile_expert = te.data_ptr(); a.tile_row0 = tr0.data_ptr(); a.tile_rows = trn.data_ptr()
+    a.n_tiles = nt.data_ptr(); a.weight = weight.data_ptr(); a.act = act.data_ptr(); a.pair_out = pair_out.data_ptr()
+    a.W = W; a.ff = ff; a.top = top
+    _check(lib, lib.tb_moe_grouped(ctypes.byref(a), _ptr(shared), c_int(shared.shape[0] if shared is not None else 0),
+                                   c_longlong(shared.stride(0) if shared is not None else 0), _ptr(gate), _ptr(out), c_int(T),
+                                   c_int(max_tiles), _stream()), "moe_grouped", 3)
+    return out
+
+
 class _MoeExpertArgs(ctypes.Structure):
     _fields_ = [("x", c_void_p), ("x_stride", c_longlong), ("gate_w", c_void_p), ("up_w", c_void_p), ("down_w", c_void_p),
                 ("idx", c_void_p), ("weight", c_void_p), ("act", c_void_p), ("shared", c_void_p), ("shared_splits", c_int),
@@ -1387,8 +1446,11 @@ def moe_experts(x: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor, down_
         if shared.dtype != torch.float32 or tuple(shared.shape[1:]) != (T, W) or shared.stride(2) != 1 or shared.stride(1) != W \
                 or gate is None:
             raise KernelError("moe: the shared expert's output must be float32 [splits, T, W] and come with its gate")
-    act = torch.empty((T * top, ff), dtype=x.dtype, device=x.device)
     out = torch.empty((T, W), dtype=torch.float32, device=x.device)
+    if x.dtype == torch.bfloat16 and T * top >= MOE_GROUPED_FROM and W % 8 == 0 and ff % 8 == 0 and x.stride(0) % 8 == 0 \
+            and x.data_ptr() % 16 == 0:
+        return _moe_grouped(x, gate_w, up_w, down_w, idx, weight, shared, gate, out)
+    act = torch.empty((T * top, ff), dtype=x.dtype, device=x.device)
     a = _MoeExpertArgs()
     a.x = x.data_ptr(); a.x_stride = x.stride(0)
     a.gate_w = gate_w.data_ptr(); a.up_w = up_w.data_ptr(); a.down_w = down_w.data_ptr()

@@ -85,7 +85,8 @@ class GatedLinearAttention(Mixer):
         proj = linear(x, self.w_in, self.rt.dtype)
         low = linear_partials(x, self.w_a1)              # [splits, T, rank] float32, added up by the decay's kernel
         y = ops.gla(proj, low, self.w_a2, self.b_a2, self.tau, self.q_scale, self.w_norm, self.eps, self.heads, self.D,
-                    self.V, state.data, ctx.seq_start, ctx.token_seq, ctx.slot_ids, ctx.batch)
+                    self.V, state.data, ctx.seq_start, ctx.token_seq, ctx.slot_ids, ctx.batch,
+                    max_seq_len=ctx.max_seq_len if ctx.is_prefill else 0)
         return linear_partials(y, self.w_o)
 
 
