@@ -19,6 +19,7 @@ MEASURED_PEAKS.json beside this file when the driver wrote it, otherwise from th
 (6.65 TB/s, 1.59 PFLOP/s).
 
     python bench.py --design divanex [--sizes small,medium,large] [--batch 8] [--context 2048]
+    python bench.py --design lofirax [--sizes small,medium,large] [--batch 8] [--context 2048]
 
 ``--design divanex`` is a measurement of its own (the default workload and its line stay as they are): Divanex
 models with random weights at a few layer sizes, a 2,048-token prompt and decode steps of ``batch`` sequences
@@ -318,6 +319,246 @@ def design_compare(args, torch):
             del engine, model
             torch.cuda.empty_cache()
         row["kernels_alone"] = design_kernels(torch, size, hbm_gbs)
+        out["sizes"][size] = row
+    clocks.__exit__()
+    out["clocks"] = clocks.summary()
+    out["kernel_errors"] = ops.kernel_errors()
+    print(json.dumps(out))
+    return 0
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# --design lofirax: the design at sizes that resemble real layers, beside Divanex (the closest model of the
+# library: recurrent and attention layers in turn, on the same host) at equal width, depth and vocabulary
+# ---------------------------------------------------------------------------------------------------------------
+# name -> (gla heads, key dim, value dim; latent heads, plain dim, rotated dim, value dim, latent rank; experts, top,
+#          expert ff, groups, kept groups, shared ff); width, depth, dense ff and vocabulary are DESIGN_SIZES'
+LOFIRAX_SIZES = {"small": (4, 128, 256, 8, 128, 64, 128, 448, 16, 4, 512, 4, 2, 1024),
+                 "medium": (8, 128, 256, 16, 128, 64, 128, 448, 32, 4, 1024, 8, 4, 2048),
+                 "large": (16, 128, 256, 32, 128, 64, 128, 448, 32, 4, 2048, 8, 4, 4096)}
+LOFIRAX_RANK = 16
+
+
+def lofirax_config(size):
+    W, L, _, _, _, ff, _, _, _, V = DESIGN_SIZES[size]
+    gh, gd, gv, lh, ld, lr, lv, lc, E, top, eff, groups, keep, sff = LOFIRAX_SIZES[size]
+    gla = {"type": "gla", "mixer": {"heads": gh, "dim": gd, "vdim": gv, "tau": 16.0, "rank": LOFIRAX_RANK},
+           "mlp": {"kind": "dense", "ff": ff}}
+    lat = {"type": "latent_attention", "mixer": {"heads": lh, "dim": ld, "rot_dim": lr, "vdim": lv, "kv_rank": lc,
+                                                 "scale": (ld + lr) ** -0.5, "rot": {"base": 500000.0, "dims": lr}},
+           "mlp": {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "top": top, "groups": {"count": groups, "keep": keep}},
+                   "shared": {"ff": sff}}}
+    # the first two layers run twice: L layer runs from L - 2 layers
+    return {"architecture": "Lofirax", "vocab": V, "width": W, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "logit_softcap": 30.0, "loop": {"start": 0, "stop": 2, "times": 2},
+            "layers": [gla if i % 2 == 0 else lat for i in range(L - 2)]}
+
+
+def lofirax_bytes_flops(cfg, tokens, ctx, batch):
+    """(weight bytes a decode step of ``batch`` sequences reads, with every matrix once and of the experts those that
+    ``batch`` tokens are expected to choose; cache and state bytes per sequence at ``ctx`` tokens; tensor-core FLOPs and
+    32-bit recurrence FLOPs of one ``tokens``-token prompt)."""
+    W, V = cfg["width"], cfg["vocab"]
+    n = len(cfg["layers"])
+    lp = cfg.get("loop")
+    runs = [1] * n
+    if lp:
+        for i in range(lp["start"], lp["stop"]):
+            runs[i] = lp["times"]
+    wb, cb, fl, rf = V * W, 0, 2 * V * W * tokens, 0
+    for L, r in zip(cfg["layers"], runs):
+        m, f = L["mixer"], L["mlp"]
+        if L["type"] == "gla":
+            HD, HV = m["heads"] * m["dim"], m["heads"] * m["vdim"]
+            per = (2 * HD + 2 * HV) * W + W * HV + LOFIRAX_RANK * (W + HD)
+            cb += r * 2 * 4 * HD * m["vdim"]                            # the state is read and written, 32-bit
+            rf += r * tokens * HD * m["vdim"] * 5
+        else:
+            H, D, R, Vd, C = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            per = H * (D + R) * W + (C + R) * W + H * (D + Vd) * C + W * H * Vd
+            cb += r * (C + R) * ctx * 2
+            fl += r * 2 * (H * (D + R) + H * Vd) * tokens * (tokens + 1) // 2
+        used = per
+        if f and f["kind"] == "dense":
+            per += 3 * f["ff"] * W
+            used = per
+        elif f:
+            E, top = f["router"]["experts"], f["router"]["top"]
+            one = 3 * f["expert"]["ff"] * W
+            sh = 3 * f["shared"]["ff"] * W + W if f.get("shared") else 0
+            used = per + E * W + sh + top * one                          # what a token's products touch
+            per += E * W + sh + one * E * (1.0 - (1.0 - top / E) ** batch)   # what a step of ``batch`` tokens is expected to read
+        wb += per
+        fl += r * 2 * tokens * used
+    return int(2 * wb), cb, fl, rf
+
+
+def lofirax_kernels(torch, size, hbm_gbs, tokens=PREFILL_TOKENS):
+    """The design's own kernels alone, each beside the like kernel of the closest model: microseconds, algorithmic
+    bytes (or FLOPs) and the fraction of the roofline.  One prompt of ``tokens`` tokens, or one token for each of 64
+    sequences at a context of 2,048."""
+    from trapetum_b200.csrc import ops
+    W, _, H, G, d, ff, mh, mp, N, _ = DESIGN_SIZES[size]
+    gh, gd, gv, lh, ld, lr, lv, lc, E, top, eff, groups, keep, sff = LOFIRAX_SIZES[size]
+    dev, bf = "cuda:0", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    T = tokens
+    out = {}
+    tc_peak = peaks()[1]
+
+    def rec(name, us, nbytes, flops=0.0, like=None, tensor_flops=0.0):
+        t_mem, t_fl = nbytes / (hbm_gbs * 1e9) * 1e6, flops / (FP32_TFLOPS_NOMINAL * 1e12) * 1e6
+        t_tc = tensor_flops / (tc_peak * 1e12) * 1e6
+        best = max(t_mem, t_fl, t_tc)
+        out[name] = {"us": round(us, 1), "bytes": int(nbytes), "roofline_us": round(best, 1), "frac": round(best / us, 3),
+                     "bound": "tensor" if best == t_tc else ("fp32" if best == t_fl else "hbm")}
+        if like:
+            out[name]["like"] = like
+    f32 = lambda *s: torch.randn(*s, device=dev)
+    pos = torch.arange(T, device=dev).int()
+    tseq = torch.zeros(T, device=dev).int()
+    ss = torch.tensor([0, T], device=dev).int()
+    slots = torch.zeros(1, device=dev).int()
+    # ---- norms
+    h, a = f32(T, W), f32(1, T, W)
+    w32, b32, wbf = torch.ones(W, device=dev), torch.zeros(W, device=dev), torch.ones(W, device=dev).to(bf)
+    rec("add_layernorm", _median_us(torch, lambda: ops.add_layernorm(h, a, w32, b32, 1e-6, bf), flush), T * W * 14, like="add_rmsnorm")
+    rec("add_rmsnorm", _median_us(torch, lambda: ops.add_rmsnorm(h, a, wbf, 1e-5, 0.0, wbf, 1e-5, 0.0, bf), flush), T * W * 14)
+    # ---- the recurrent mixers: whole prompt
+    HD, HV = gh * gd, gh * gv
+    proj = torch.randn(T, 2 * HD + 2 * HV, device=dev).to(bf)
+    low = f32(1, T, LOFIRAX_RANK)
+    a2, a2b, nw = f32(HD, LOFIRAX_RANK) * .3, f32(HD) + 2, torch.ones(gv, device=dev)
+    gstate = torch.zeros(1, HD * gv, device=dev)
+    rec("gla (decay, scan, gated norm)",
+        _median_us(torch, lambda: ops.gla(proj, low, a2, a2b, 16.0, gd ** -0.5, nw, 1e-6, gh, gd, gv, gstate, ss, tseq, slots, 1, max_seq_len=T), flush),
+        T * ((2 * HD + 2 * HV) * 2 + HD * 4 * 2 + HV * 4 * 2 + HV * 2), flops=T * HD * gv * 5.0, like="mamba2 (conv, scan, gated norm)")
+    inner, ch = mh * mp, mh * mp + 2 * N
+    mproj = torch.randn(T, inner + ch, device=dev).to(bf)
+    dtr = f32(T, mh)
+    cw, cb, dtb, Al, D, mnw = f32(ch, 4) * .3, f32(ch) * .1, f32(mh) - 1, f32(mh) * .5, f32(mh), f32(inner)
+    mstate = torch.zeros(1, ops.mamba2_state_size(mh, mp, N, 1, 4), device=dev)
+    rec("mamba2 (conv, scan, gated norm)",
+        _median_us(torch, lambda: ops.mamba2(mproj, dtr, mh, mp, N, 1, 4, 1, cw, cb, dtb, Al, D, mnw, 1e-5, mstate, ss, tseq, slots, 1, False,
+                                             max_seq_len=T), flush),
+        T * (ch * 2 * 3 + inner * 2 + inner * 4 * 2 + inner * 2), flops=T * inner * N * 5.0)
+    # ---- one token for each of 64 sequences: the states are read and written once
+    B = 64
+    ss1, tseq1 = torch.arange(B + 1, device=dev).int(), torch.arange(B, device=dev).int()
+    proj1, low1 = torch.randn(B, 2 * HD + 2 * HV, device=dev).to(bf), f32(1, B, LOFIRAX_RANK)
+    gstate64 = torch.zeros(B, HD * gv, device=dev)
+    rec("gla, one token for each of 64 sequences",
+        _median_us(torch, lambda: ops.gla(proj1, low1, a2, a2b, 16.0, gd ** -0.5, nw, 1e-6, gh, gd, gv, gstate64, ss1, tseq1, tseq1, B), flush),
+        gstate64.numel() * 8, like="mamba2, one token for each of 64 sequences")
+    mproj1, dtr1 = torch.randn(B, inner + ch, device=dev).to(bf), f32(B, mh)
+    mstate64 = torch.zeros(B, ops.mamba2_state_size(mh, mp, N, 1, 4), device=dev)
+    rec("mamba2, one token for each of 64 sequences",
+        _median_us(torch, lambda: ops.mamba2(mproj1, dtr1, mh, mp, N, 1, 4, 1, cw, cb, dtb, Al, D, mnw, 1e-5, mstate64, ss1, tseq1, tseq1, B, True), flush),
+        mstate64.numel() * 8)
+    # ---- what stands between the attention's products and its kernel
+    KD = lc + lr
+    pages = (T + 63) // 64
+    pool = torch.zeros(pages, 1, 64, KD, dtype=bf, device=dev)
+    table = torch.arange(pages, device=dev).int().view(1, pages)
+    part = f32(1, T, KD)
+    inv = torch.rand(lr // 2, device=dev)
+    cn = torch.ones(lc, device=dev)
+    rec("latent_rows", _median_us(torch, lambda: ops.latent_rows(part, cn, 1e-6, inv, lr, lc, lr, pos, tseq, pool, table, bf), flush),
+        T * KD * (4 + 2 + 2), like="headnorm_kv")
+    la = torch.tensor([T], device=dev).int()
+    kp = torch.zeros(pages, G, 64, d, dtype=bf, device=dev)
+    vp = torch.zeros_like(kp)
+    hpart = f32(1, T, (H + G) * d)
+    rec("headnorm_kv", _median_us(torch, lambda: ops.headnorm_kv(hpart, H, G, d, bf, True, True, True, 1e-5, 0.5, 64, pos, tseq, la, kp, vp, table, 0), flush),
+        hpart.numel() * 4 + T * (H + 2 * G) * d * 2 + T * 2 * G * d * 2)
+    # ---- causal attention of the prompt
+    hd = next(n for n in (64, 128, 256) if n >= max(ld + lr, lv))       # as the part pads it in bfloat16
+    q, k, v = (torch.randn(T, lh * hd, device=dev).to(bf) for _ in range(3))
+    sink = torch.zeros(lh, device=dev)
+    rec("attention with a sink (prefill)", _median_us(torch, lambda: ops.attn_prefill_sink(q, k, v, ss, tseq, lh, hd, 0.07, sink, T, [T]), flush),
+        T * lh * hd * 2 * 4, tensor_flops=2.0 * lh * (ld + lr + lv) * T * (T + 1) / 2, like="attention (prefill)")
+    q2 = torch.randn(T, (H + 2 * G) * d, device=dev).to(bf)
+    rec("attention (prefill)",
+        _median_us(torch, lambda: ops.attn_prefill(q2[:, :H * d], q2[:, H * d:(H + G) * d], q2[:, (H + G) * d:], ss, tseq, H, G, d,
+                                                   d ** -0.5, 30.0, 0, T, [T], {}), flush),
+        T * (H + 2 * G) * d * 2 + T * H * d * 2, tensor_flops=4.0 * H * d * T * (T + 1) / 2)
+    # ---- decode attention: 64 sequences at a context of 2,048
+    ctx = 2048
+    pg = ctx // 64
+    lpool = torch.randn(B * pg, 1, 64, KD, device=dev).to(bf)
+    ltab = torch.arange(B * pg, device=dev).int().view(B, pg)
+    lens = torch.full((B,), ctx, device=dev).int()
+    ql = torch.randn(B, lh * KD, device=dev).to(bf)
+    rec("latent_decode", _median_us(torch, lambda: ops.latent_decode(ql, lpool, ltab, lens, sink, lh, lc, lr, 0.07, ctx), flush),
+        lpool.numel() * 2, like="attention (decode)")
+    kp2 = torch.randn(B * pg, G, 64, d, device=dev).to(bf)
+    vp2 = torch.randn(B * pg, G, 64, d, device=dev).to(bf)
+    qd = torch.randn(B, H * d, device=dev).to(bf)
+    rec("attention (decode)", _median_us(torch, lambda: ops.attn_decode(qd, kp2, vp2, ltab, lens, H, G, d, d ** -0.5, 30.0, 0, 0, ctx, 0), flush),
+        kp2.numel() * 4)
+    # ---- the experts: routing, then the grouped products; beside a dense gated feed-forward's two products
+    x = torch.randn(T, W, device=dev).to(bf)
+    corr = f32(E) * .1
+    logits = f32(1, T, (E + 16) // 16 * 16)
+    rec("moe_route", _median_us(torch, lambda: ops.moe_route(logits, E, corr, True, top, groups, keep, 2, 1e-20), flush),
+        logits.numel() * 4 + T * top * 8, like="add_rmsnorm")
+    idx, wt, gate = ops.moe_route(logits, E, corr, True, top, groups, keep, 2, 1e-20)
+    gw, uw, dw = (torch.randn(E, a_, b_, device=dev).to(bf) * .02 for a_, b_ in ((eff, W), (eff, W), (W, eff)))
+    rec("experts (grouped products)", _median_us(torch, lambda: ops.moe_experts(x, gw, uw, dw, idx, wt), flush),
+        3 * E * eff * W * 2 + T * W * 2, tensor_flops=2.0 * T * top * 3 * eff * W, like="gated feed-forward (two products)")
+    wgu = ops.interleave_gate_up(torch.randn(ff, W, device=dev).to(bf) * .02, torch.randn(ff, W, device=dev).to(bf) * .02)
+    wdn = torch.randn(W, ff, device=dev).to(bf) * .02
+
+    def dense_ff():
+        act = ops.gemm_tc(x, wgu, bf, gated_act="gelu_tanh")
+        return ops.gemm_tc(act, wdn, torch.float32, partials=True)
+    rec("gated feed-forward (two products)", _median_us(torch, dense_ff, flush), 3 * ff * W * 2 + T * W * 2,
+        tensor_flops=2.0 * T * 3 * ff * W)
+    return out
+
+
+def lofirax_compare(args, torch):
+    """Prints one JSON line: per size, Lofirax and the Divanex model of equal width, depth and vocabulary (prefill of
+    one 2,048-token prompt, decode at ``batch`` x ``context``), with bytes, FLOPs and roofline fractions, and the
+    design's kernels alone beside their like kernels."""
+    import trapetum_b200 as tb
+    from trapetum_b200.csrc import ops
+    hbm_gbs, bf16_tflops, peak_src = peaks()
+    warmup = max(3, args.warmup)
+    ctx, batch = args.context, args.batch
+    sizes = [s for s in args.sizes.split(",") if s in DESIGN_SIZES]
+    out = {"design": "lofirax", "beside": "divanex", "sizes": {},
+           "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops, "source": peak_src, "fp32_tflops_nominal": FP32_TFLOPS_NOMINAL},
+           "dtype": "bf16", "data": "synthetic (random weights, random token ids)", "batch": batch, "context": ctx,
+           "timing": "CUDA events; decode: median of five regions of --steps steps; kernels alone: a 256 MB buffer is written "
+                     "between timed launches (larger than L2)"}
+    clocks = ClockSampler()
+    clocks.__enter__()
+    for size in sizes:
+        row = {}
+        for which in ("lofirax", "divanex"):
+            cfg = lofirax_config(size) if which == "lofirax" else divanex_config(size)
+            V = cfg["vocab"]
+            model = tb.random_model(cfg, 7, 0.02, 0.1, "bfloat16", "cuda:0", host="python")
+            engine = tb.Engine(model, max_tokens=batch * (ctx + 64), max_slots=batch)
+            random_cache(engine)
+            pms, hms, wms = time_prefill(engine, torch, PREFILL_TOKENS, V, reps=5, warmup=warmup)
+            r = time_decode(engine, torch, [ctx] * batch, args.steps, warmup, V, clocks=clocks)
+            wb, cb, fl, rf = (lofirax_bytes_flops if which == "lofirax" else divanex_bytes_flops)(cfg, PREFILL_TOKENS, ctx, batch)
+            nbytes = wb + batch * cb
+            pre_ideal = fl / (bf16_tflops * 1e12) + rf / (FP32_TFLOPS_NOMINAL * 1e12)
+            row[which] = {
+                "prefill": {"tokens": PREFILL_TOKENS, "ms": round(pms, 3), "tok_s": round(PREFILL_TOKENS * 1e3 / pms, 1),
+                            "tensor_flops": fl, "fp32_recurrence_flops": rf, "frac_of_roofline": round(pre_ideal * 1e3 / pms, 4)},
+                "decode": {"ms": r["ms"], "tok_s": round(batch * 1e3 / r["ms"], 1), "bytes": nbytes,
+                           "gbs": round(nbytes / (r["ms"] * 1e-3) / 1e9, 1),
+                           "frac_of_hbm": round(nbytes / (r["ms"] * 1e-3) / 1e9 / hbm_gbs, 4), "launches": r["launches"]},
+            }
+            engine.check_kernels()
+            del engine, model
+            torch.cuda.empty_cache()
+        if not args.no_points:
+            row["kernels_alone"] = lofirax_kernels(torch, size, hbm_gbs)
         out["sizes"][size] = row
     clocks.__exit__()
     out["clocks"] = clocks.summary()
@@ -674,8 +915,9 @@ def main() -> int:
     ap.add_argument("--leave-out", action="store_true",
                     help="instead of the bench line: the decode step re-timed with one kind of launch left out at a "
                          "time (its results are then wrong; only its time is of interest), one line per kind")
-    ap.add_argument("--design", default=None, choices=["divanex"],
-                    help="instead of the bench line: this design at the layer sizes of --sizes beside Gemma-2 at equal size")
+    ap.add_argument("--design", default=None, choices=["divanex", "lofirax"],
+                    help="instead of the bench line: this design at the layer sizes of --sizes beside the library's closest "
+                         "model at equal size (divanex beside Gemma-2, lofirax beside divanex)")
     ap.add_argument("--sizes", default="small,medium,large", help="with --design: which of small, medium, large")
     ap.add_argument("--gemm-compare", type=int, default=0, metavar="TOKENS",
                     help="instead of the bench line: the four products of a layer of --model at TOKENS tokens, this "
@@ -697,7 +939,7 @@ def main() -> int:
     if args.design:
         if args.context == 8192:
             args.context = 2048
-        return design_compare(args, torch)
+        return lofirax_compare(args, torch) if args.design == "lofirax" else design_compare(args, torch)
     if args.gemm_compare:
         return gemm_compare(MODELS[args.model], torch, args.gemm_compare, peaks()[1])
     from trapetum_b200 import Engine

@@ -124,7 +124,8 @@ def test_gated_linear_attention_between_its_products(H, D, V, rank, lens, dtype)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H, C, R, dims", [(2, 40, 8, 8), (3, 24, 16, 8), (4, 96, 32, 32), (1, 200, 64, 64)])
+@pytest.mark.parametrize("H, C, R, dims", [(2, 40, 8, 8), (3, 24, 16, 8), (4, 96, 32, 32), (1, 200, 64, 64), (20, 128, 32, 32),
+                                           (8, 448, 64, 64), (5, 80, 0, 0)])
 def test_latent_rows_and_decoding_over_them(H, C, R, dims, dtype):
     """Rows written at positions across three pages (in pages that are out of order), then one query per sequence."""
     from trapetum_b200.csrc import ops
@@ -174,14 +175,14 @@ def test_per_head_products_and_attention_with_a_sink(dtype):
     x, w = torch.randn(T, H * i + 8, generator=g).to(dt), torch.randn(H, o, i, generator=g).to(dt)
     y = ops.head_linear(dev(x)[:, 8:], dev(w), H)
     near(y.view(T, H, o), torch.einsum("thi,hoi->tho", x[:, 8:].double().reshape(T, H, i), w.double()), dtype, "per-head product")
-    for hd in (24, 48):                                         # the generic kernel; the tensor-core kernel in bfloat16
+    for hd in (24, 48, 64, 128):                                # the generic kernel; in bfloat16 the mma.sync and the tcgen05 kernels
         lens = [70, 3, 129]
         T = sum(lens)
         q, k, v = (torch.randn(T, H * hd, generator=g).to(dt) for _ in range(3))
         sink = torch.tensor([-2.0, 0.7, 9.0])
         starts = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
         tok_seq = torch.repeat_interleave(torch.arange(3), torch.tensor(lens)).int()
-        out = ops.attn_prefill_sink(dev(q), dev(k), dev(v), dev(starts), dev(tok_seq), H, hd, 0.4, dev(sink), max(lens))
+        out = ops.attn_prefill_sink(dev(q), dev(k), dev(v), dev(starts), dev(tok_seq), H, hd, 0.4, dev(sink), max(lens), lens)
         for b in range(3):
             a, e = int(starts[b]), int(starts[b + 1])
             qq, kk, vv = (z[a:e].double().view(e - a, H, hd) for z in (q, k, v))
@@ -201,7 +202,9 @@ def test_router_choices_and_weights(E, top, groups, keep):
     x = torch.randn(T, W, generator=g)
     t = {"router": torch.randn(E, W, generator=g) / 3, "correction": torch.randn(E, generator=g) - 1.5}   # choice scores below zero too
     sg = torch.randn(W, generator=g) / 3
-    idx, wt, gate = ops.moe_route(dev(x), dev(t["router"]), dev(t["correction"]), dev(sg), top, groups, keep, 2, 1e-20)
+    z = torch.cat([x.double() @ t["router"].double().T, (x.double() @ sg.double())[:, None], torch.zeros(T, 3, dtype=F)], dim=1)
+    parts = torch.stack([0.3 * z, 0.7 * z]).float()               # two partial sums, columns past the gate's unused
+    idx, wt, gate = ops.moe_route(dev(parts), E, dev(t["correction"]), True, top, groups, keep, 2, 1e-20)
     r = {"experts": E, "top": top}
     if groups > 1:
         r["groups"] = {"count": groups, "keep": keep}

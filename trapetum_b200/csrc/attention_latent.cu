@@ -248,6 +248,191 @@ __global__ void latent_combine_kernel(LatentDecodeArgs a) {
     }
 }
 
+// ---------------------------------------------------------------------------
+// The same decode on tensor cores (bfloat16): one CTA takes up to 16 heads of a sequence and a range of its
+// keys, so that a cached row is fetched once for all of them.  Rows arrive 32 at a time (half a page, one
+// contiguous piece of memory) by cp.async into a two-stage ring; S = Q' K^T with the heads as the 16
+// rows of mma.sync m16n8k16 (each warp 8 of the 32 keys), the softmax of a head's 32 scores by one warp (four heads
+// each), then O += P C with every warp taking a share of the latent's columns.  Partial (max, sum, o) go to the
+// scratch that latent_combine_kernel folds (it also adds the sink).
+// ---------------------------------------------------------------------------
+constexpr int LD_BN = 32, LD_HEADS = 16, LD_WARPS = 4;
+
+__device__ __forceinline__ uint32_t ld_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ld_cp16(void* dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ld_smem(dst)), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void ld_ldsm4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ld_ldsm2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void ld_ldsm4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ld_mma(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// NP: pairs of 8-column tiles of the latent per warp (C <= NP * 64)
+template <int NP>
+__global__ void __launch_bounds__(LD_WARPS * 32) latent_decode_mma_kernel(LatentDecodeArgs a) {
+    pdl_launch_dependents();
+    extern __shared__ __align__(16) unsigned char sm[];
+    const int KD = a.C + a.R, C = a.C;
+    const int pitch = KD * 2 + 16;
+    unsigned char* q_s = sm;                                        // [16][pitch]
+    unsigned char* k_s = q_s + LD_HEADS * pitch;                    // [2][LD_BN][pitch]
+    float* s_s = (float*)(k_s + 2 * LD_BN * pitch);                 // [16][LD_BN]
+    unsigned char* p_s = (unsigned char*)(s_s + LD_HEADS * LD_BN);  // [16][LD_BN * 2 + 16]
+    float* corr_s = (float*)(p_s + LD_HEADS * (LD_BN * 2 + 16));    // [16]
+    constexpr int PP = LD_BN * 2 + 16;
+    const int b = blockIdx.x, hg = blockIdx.y, split = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h0 = hg * LD_HEADS, nh = min(LD_HEADS, a.heads - h0);
+    pdl_wait();
+    const int len = a.len_after[b];
+    int per = (len + a.n_splits - 1) / a.n_splits;
+    per = (per + LD_BN - 1) / LD_BN * LD_BN;
+    const int beg = split * per, end = min(len, beg + per);
+    const int* pt = a.page_table + (size_t)b * a.pt_stride;
+    const bf16* pool = (const bf16*)a.pool;
+    const int chunks = KD / 8;                                      // 16-byte pieces of a row
+    auto load = [&](int stage, int j0) {
+        const bf16* src = pool + ((size_t)pt[j0 / a.page_rows] * a.page_rows + (j0 % a.page_rows)) * KD;
+        unsigned char* dst = k_s + (size_t)stage * LD_BN * pitch;
+        for (int c = threadIdx.x; c < LD_BN * chunks; c += LD_WARPS * 32) {
+            const int r = c / chunks, ch = c % chunks;
+            ld_cp16(dst + r * pitch + ch * 16, src + (size_t)r * KD + ch * 8, j0 + r < end);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (beg < end) load(0, beg);
+    {   // the queries of this CTA's heads (rows past the last head: zeros)
+        const bf16* q = (const bf16*)a.q + (size_t)b * a.q_stride + (size_t)h0 * KD;
+        for (int c = threadIdx.x; c < LD_HEADS * chunks; c += LD_WARPS * 32) {
+            const int r = c / chunks, ch = c % chunks;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < nh) v = *(const uint4*)(q + (size_t)r * KD + ch * 8);
+            *(uint4*)(q_s + r * pitch + ch * 16) = v;
+        }
+    }
+    float o[NP * 2][4];
+#pragma unroll
+    for (int n = 0; n < NP * 2; n++) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m_run[4], l_run[4];                                       // of heads 4 * warp + i (every lane holds a copy)
+#pragma unroll
+    for (int i = 0; i < 4; i++) { m_run[i] = -INFINITY; l_run[i] = 0.f; }
+    const int n_tiles = beg < end ? (end - beg + LD_BN - 1) / LD_BN : 0;
+    for (int it = 0; it < n_tiles; it++) {
+        const int j0 = beg + it * LD_BN;
+        if (it + 1 < n_tiles) { load((it + 1) & 1, j0 + LD_BN); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        const unsigned char* kt = k_s + (size_t)(it & 1) * LD_BN * pitch;
+        // ---- scores of this warp's 8 keys for all 16 heads
+        float sc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int ks = 0; ks < KD / 16; ks++) {
+            uint32_t fa[4], b0, b1;
+            ld_ldsm4(ld_smem(q_s + (lane & 15) * pitch + (ks * 16 + (lane >> 4) * 8) * 2), fa[0], fa[1], fa[2], fa[3]);
+            ld_ldsm2(ld_smem(kt + (warp * 8 + (lane & 7)) * pitch + (ks * 16 + ((lane >> 3) & 1) * 8) * 2), b0, b1);
+            ld_mma(sc, fa, b0, b1);
+        }
+        {
+            const int r = lane >> 2, cc = warp * 8 + (lane & 3) * 2;
+            s_s[r * LD_BN + cc] = sc[0] * a.scale; s_s[r * LD_BN + cc + 1] = sc[1] * a.scale;
+            s_s[(r + 8) * LD_BN + cc] = sc[2] * a.scale; s_s[(r + 8) * LD_BN + cc + 1] = sc[3] * a.scale;
+        }
+        __syncthreads();
+        // ---- softmax of four heads per warp over the tile's 32 keys (one key per lane)
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int r = warp * 4 + i;
+            const float v = (j0 + lane < end) ? s_s[r * LD_BN + lane] : -INFINITY;
+            const float mn = fmaxf(m_run[i], warp_max(v));
+            const float corr = (m_run[i] == -INFINITY) ? 0.f : expf(m_run[i] - mn);
+            const float p = (v == -INFINITY) ? 0.f : expf(v - mn);
+            l_run[i] = l_run[i] * corr + warp_sum(p);
+            m_run[i] = mn;
+            *(bf16*)(p_s + r * PP + lane * 2) = __float2bfloat16_rn(p);
+            if (lane == 0) corr_s[r] = corr;
+        }
+        __syncthreads();
+        // ---- O = O * corr + P C, this warp's share of the latent's columns
+        const float ca = corr_s[lane >> 2], cb = corr_s[(lane >> 2) + 8];
+        uint32_t pa[LD_BN / 16][4];
+#pragma unroll
+        for (int kk = 0; kk < LD_BN / 16; kk++)
+            ld_ldsm4(ld_smem(p_s + (lane & 15) * PP + (kk * 16 + (lane >> 4) * 8) * 2), pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3]);
+#pragma unroll
+        for (int j = 0; j < NP; j++) {
+            const int col0 = (j * LD_WARPS + warp) * 16;
+            if (col0 >= C) continue;
+            float* oa = o[2 * j]; float* ob = o[2 * j + 1];
+            oa[0] *= ca; oa[1] *= ca; oa[2] *= cb; oa[3] *= cb; ob[0] *= ca; ob[1] *= ca; ob[2] *= cb; ob[3] *= cb;
+#pragma unroll
+            for (int kk = 0; kk < LD_BN / 16; kk++) {
+                uint32_t b0, b1, b2, b3;
+                ld_ldsm4_t(ld_smem(kt + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * pitch + (col0 + (lane >> 4) * 8) * 2), b0, b1, b2, b3);
+                ld_mma(oa, pa[kk], b0, b1);
+                ld_mma(ob, pa[kk], b2, b3);
+            }
+        }
+        __syncthreads();                                            // the load after next overwrites this stage; s_s and p_s are free
+    }
+    // ---- partial results: [b][h][split][C + 2]
+    const int ra = lane >> 2, rb = ra + 8;
+#pragma unroll
+    for (int j = 0; j < NP; j++) {
+        const int col0 = (j * LD_WARPS + warp) * 16;
+        if (col0 >= C) continue;
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int col = col0 + half * 8 + (lane & 3) * 2;
+            const float* acc = o[2 * j + half];
+            if (ra < nh) { float* p = a.partial + (((size_t)b * a.heads + h0 + ra) * a.n_splits + split) * (C + 2); p[col] = acc[0]; p[col + 1] = acc[1]; }
+            if (rb < nh) { float* p = a.partial + (((size_t)b * a.heads + h0 + rb) * a.n_splits + split) * (C + 2); p[col] = acc[2]; p[col + 1] = acc[3]; }
+        }
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int r = warp * 4 + i;
+            if (r < nh) { float* p = a.partial + (((size_t)b * a.heads + h0 + r) * a.n_splits + split) * (C + 2); p[C] = m_run[i]; p[C + 1] = l_run[i]; }
+        }
+    }
+}
+
+extern "C" int tb_latent_decode_mma_takes(int C, int R) {
+    return C > 0 && C % 16 == 0 && (C + R) % 16 == 0 && C <= 512 && (C + R) <= 1024;
+}
+
+extern "C" int tb_latent_decode_mma(const LatentDecodeArgs* args, int batch, cudaStream_t stream) {
+    if (batch <= 0) return 0;
+    const LatentDecodeArgs& a = *args;
+    if (!tb_latent_decode_mma_takes(a.C, a.R)) return tb_refuse("latent_decode_mma: C=%d R=%d (multiples of 16, C <= 512)", a.C, a.R);
+    if (a.partial == nullptr || a.n_splits < 1 || a.n_splits > 65535 || a.out_dim < a.C || a.page_rows % LD_BN)
+        return tb_refuse("latent_decode_mma: n_splits=%d needs scratch; pages of %d rows", a.n_splits, a.page_rows);
+    if (((uintptr_t)a.q & 15) || (a.q_stride % 8) || ((uintptr_t)a.pool & 15)) return tb_refuse("latent_decode_mma: rows must be 16-byte aligned");
+    const int KD = a.C + a.R, pitch = KD * 2 + 16;
+    const size_t smem = (size_t)LD_HEADS * pitch + 2 * (size_t)LD_BN * pitch + LD_HEADS * LD_BN * 4 + LD_HEADS * (LD_BN * 2 + 16) + LD_HEADS * 4;
+    const int np = (a.C + 63) / 64;
+    dim3 grid(batch, (a.heads + LD_HEADS - 1) / LD_HEADS, a.n_splits);
+#define LD_MMA(N) do { \
+        static bool set = false; \
+        if (!set) { cudaError_t e = cudaFuncSetAttribute(latent_decode_mma_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+                    if (e != cudaSuccess) return (int)e; set = true; } \
+        tb_launch(latent_decode_mma_kernel<N>, dim3(grid), dim3(LD_WARPS * 32), smem, stream, a); } while (0)
+    if (np <= 2) LD_MMA(2); else if (np <= 4) LD_MMA(4); else LD_MMA(8);
+    int st = tb_launch_status();
+    if (st) return st;
+    tb_launch(latent_combine_kernel<bf16>, dim3(batch, a.heads), dim3(128), 0, stream, a);
+    return tb_launch_status();
+}
+
 extern "C" int tb_latent_decode(const LatentDecodeArgs* args, int dtype, int batch, cudaStream_t stream) {
     if (batch <= 0) return 0;
     const LatentDecodeArgs& a = *args;

@@ -63,6 +63,7 @@ struct PrefillTcArgs {
     bf16* out;                     // [T, n_heads * HD]
     int n_heads, n_kv_heads, window;
     float scale, cap;
+    const float* sink;             // [n_heads] or null: the softmax denominator also holds exp(sink_h)
 };
 
 __device__ __forceinline__ float ex2f(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
@@ -370,7 +371,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
         if (ok) {
             tc_fence_after();
-            const float inv = 1.f / (row_l[0][r] + row_l[1][r]);
+            float denom = row_l[0][r] + row_l[1][r];
+            if (a.sink != nullptr) {
+                // both sums stand at the reference of the row's last block (scores are in log2 units)
+                const float fin = row_ref[(nblocks - 1) & 1][r];
+                if (fin != -INFINITY) denom += ex2f(a.sink[h] * 1.4426950408889634f - fin);
+            }
+            const float inv = 1.f / denom;
             bf16* orow = a.out + ((size_t)(s0 + i) * a.n_heads + h) * HD;
 #pragma unroll 1
             for (int c0 = group * (HD / 2); c0 < (group + 1) * (HD / 2); c0 += 32) {   // each group writes half of the columns
@@ -431,9 +438,9 @@ static int make_map(CUtensorMap* m, const void* base, long long rows, long long 
 
 extern "C" int tb_attn_prefill_tc_head_dim() { return HD; }
 
-extern "C" int tb_attn_prefill_tc(const void* q, const void* k, const void* v, long long q_stride, long long kv_stride,
+extern "C" int tb_attn_prefill_tc_ex(const void* q, const void* k, const void* v, long long q_stride, long long kv_stride,
                                   const int* seq_start, void* out, int n_tokens, int batch, int max_seq_len, int n_heads,
-                                  int n_kv_heads, int hd, float scale, float cap, int window, cudaStream_t stream) {
+                                  int n_kv_heads, int hd, float scale, float cap, int window, const float* sink, cudaStream_t stream) {
     if (batch <= 0 || max_seq_len <= 0) return 0;
     if (hd != HD) return tb_refuse("attn_prefill_tc: this library is built for head_dim %d, got %d", HD, hd);
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads)
@@ -448,7 +455,7 @@ extern "C" int tb_attn_prefill_tc(const void* q, const void* k, const void* v, l
     PrefillTcArgs a;
     a.q = (const bf16*)q; a.q_stride = q_stride; a.n_tokens = n_tokens;
     a.seq_start = seq_start; a.out = (bf16*)out;
-    a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.window = window; a.scale = scale; a.cap = cap;
+    a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.window = window; a.scale = scale; a.cap = cap; a.sink = sink;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -458,6 +465,13 @@ extern "C" int tb_attn_prefill_tc(const void* q, const void* k, const void* v, l
     dim3 grid(n_heads, batch, (max_seq_len + BM - 1) / BM);
     tb_launch(attn_prefill_tc_kernel, grid, dim3(320), SMEM_BYTES, stream, mk, mv, a);
     return tb_launch_status();
+}
+
+extern "C" int tb_attn_prefill_tc(const void* q, const void* k, const void* v, long long q_stride, long long kv_stride,
+                                  const int* seq_start, void* out, int n_tokens, int batch, int max_seq_len, int n_heads,
+                                  int n_kv_heads, int hd, float scale, float cap, int window, cudaStream_t stream) {
+    return tb_attn_prefill_tc_ex(q, k, v, q_stride, kv_stride, seq_start, out, n_tokens, batch, max_seq_len, n_heads, n_kv_heads,
+                                 hd, scale, cap, window, nullptr, stream);
 }
 
 extern "C" int tb_attn_prefill_tc_error() {

@@ -15,10 +15,11 @@
 // 32-bit throughout: z, the decay, the state, o and the norm.  q, k, v and g arrive in the activations'
 // dtype (they are products) and are widened on the way in.
 //
-// The scan: one CTA = 32 value channels of one head of one sequence, eight warps that each own an
-// eighth of the key channels; a thread keeps its part of one column of S in registers.  q, k and the
-// decay of eight tokens at a time are staged in shared memory (every thread of a warp reads the same
-// word: a broadcast); the warps' partial outputs of those eight tokens meet in shared memory once per tile.
+// The scan: one CTA = 64 value channels of one head of one sequence (or of a chunk in time of it), eight warps
+// that each own an eighth of the key channels; a thread keeps its part of two columns of S in registers.  q, k
+// and the decay of eight tokens at a time are staged in shared memory (every thread of a warp reads the same
+// 16-byte word: a broadcast that serves both columns), the next eight are on their way through registers
+// meanwhile; the warps' partial outputs of a tile meet in shared memory once per tile.
 #include "common.cuh"
 
 TB_EXPORT_ERROR()
@@ -41,26 +42,41 @@ struct GlaArgs {
     int chunk_len, n_chunks;
 };
 
-__global__ void gla_decay_kernel(GlaArgs a) {
+constexpr int GLA_DECAY_TOK = 32;
+
+// 32 tokens and 256 channels per CTA: a thread owns a channel, keeps the 32 sums in registers and reads its row of A2 once.
+__global__ void __launch_bounds__(256) gla_decay_kernel(GlaArgs a) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float low_s[];                  // [rank]: A1 x of this token
-    const int t = blockIdx.x;
+    extern __shared__ float low_s[];                  // [32][rank]: A1 x of these tokens
+    const int t0 = blockIdx.x * GLA_DECAY_TOK, nt = min(GLA_DECAY_TOK, a.n_tokens - t0);
     const int HD = a.heads * a.D;
-    for (int r = threadIdx.x; r < a.rank; r += blockDim.x) {
+    for (int i = threadIdx.x; i < GLA_DECAY_TOK * a.rank; i += blockDim.x) {
+        const int tt = i / a.rank, r = i % a.rank;
         float v = 0.f;
-        for (int s = 0; s < a.a1_splits; s++) v += a.a1[(size_t)s * a.a1_split_stride + (size_t)t * a.rank + r];
-        low_s[r] = v;
+        if (tt < nt)
+            for (int s = 0; s < a.a1_splits; s++) v += a.a1[(size_t)s * a.a1_split_stride + (size_t)(t0 + tt) * a.rank + r];
+        low_s[i] = v;
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < HD; c += blockDim.x) {
-        const float* w = a.a2 + (size_t)c * a.rank;
-        float z = 0.f;
-        for (int r = 0; r < a.rank; r++) z = fmaf(w[r], low_s[r], z);
-        z += a.a2_bias[c];
-        const float x = -z;                           // log sigmoid(z) = -softplus(-z)
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= HD) return;
+    float z[GLA_DECAY_TOK];
+    const float bias = a.a2_bias[c];
+#pragma unroll
+    for (int tt = 0; tt < GLA_DECAY_TOK; tt++) z[tt] = 0.f;
+    const float* w = a.a2 + (size_t)c * a.rank;
+    for (int r = 0; r < a.rank; r++) {
+        const float wr = w[r];
+#pragma unroll
+        for (int tt = 0; tt < GLA_DECAY_TOK; tt++) z[tt] = fmaf(wr, low_s[tt * a.rank + r], z[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < GLA_DECAY_TOK; tt++) {
+        if (tt >= nt) break;
+        const float x = -(z[tt] + bias);               // log sigmoid(z) = -softplus(-z)
         const float sp = x > 20.f ? x : log1pf(expf(x));
-        a.decay[(size_t)t * HD + c] = expf(-sp * a.inv_tau);
+        a.decay[(size_t)(t0 + tt) * HD + c] = expf(-sp * a.inv_tau);
     }
 }
 
@@ -70,77 +86,128 @@ constexpr int GLA_WARPS = 8;       // slices of the key channels
 // MODE 0: a sequence from the state its slot holds to the state it leaves there, with outputs.
 // MODE 1: a chunk from a zero state, without outputs: its end state and the product of its decays (for the fold).
 // MODE 2: a chunk from the start state the fold left, with outputs; the last chunk leaves the sequence's state.
+constexpr int GLA_VT = 64;         // value channels per CTA: two per thread, so that a word of q, k or the decay serves two updates
+
 template <typename T, int DPT, int MODE>
-__global__ void __launch_bounds__(GLA_WARPS * 32) gla_scan_kernel(GlaArgs a) {
+__global__ void __launch_bounds__(GLA_WARPS * 32, 2) gla_scan_kernel(GlaArgs a) {
     pdl_launch_dependents();
     constexpr int DP = DPT * GLA_WARPS;                // key channels, padded
-    __shared__ float q_s[GLA_TT][DP], k_s[GLA_TT][DP], d_s[GLA_TT][DP];
-    __shared__ float v_s[GLA_TT][32];
-    __shared__ float part_s[GLA_TT][GLA_WARPS][32];
+    constexpr int PER = (GLA_TT * DP + GLA_WARPS * 32 - 1) / (GLA_WARPS * 32);   // staged (token, channel) places per thread
+    __shared__ __align__(16) float q_s[GLA_TT][DP], k_s[GLA_TT][DP], d_s[GLA_TT][DP];
+    __shared__ float v_s[GLA_TT][GLA_VT];
+    __shared__ float part_s[GLA_TT][GLA_WARPS][GLA_VT];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int h = blockIdx.y;
     const int b = MODE == 0 ? blockIdx.z : blockIdx.z / a.n_chunks;
     const int chunk = MODE == 0 ? 0 : blockIdx.z % a.n_chunks;
     const int D = a.D, V = a.V, HD = a.heads * D, HV = a.heads * V;
-    const int v0 = blockIdx.x * 32, vch = v0 + lane;
-    const bool v_ok = vch < V;
+    const int v0 = blockIdx.x * GLA_VT;
+    const int vc[2] = {v0 + lane, v0 + lane + 32};
+    const bool v_ok[2] = {vc[0] < V, vc[1] < V};
     pdl_wait();
     int s0 = a.seq_start[b], s1 = a.seq_start[b + 1];
     const int seq_end = s1;
     if (MODE != 0) { s0 = min(s1, s0 + chunk * a.chunk_len); s1 = min(s1, s0 + a.chunk_len); }
     float* st = a.state + (size_t)a.slot_ids[b] * a.state_stride + (size_t)h * D * V;
     float* cst = MODE == 0 ? nullptr : a.chunk_state + ((size_t)b * a.n_chunks + chunk) * a.heads * D * V + (size_t)h * D * V;
-    float S[DPT], P[DPT];
+    float S[2][DPT], P[MODE == 1 ? DPT : 1];
 #pragma unroll
     for (int j = 0; j < DPT; j++) {
         const int d = warp * DPT + j;
         const float* from = MODE == 2 ? cst : st;
-        S[j] = (MODE != 1 && d < D && v_ok) ? from[(size_t)d * V + vch] : 0.f;
-        P[j] = 1.f;
+#pragma unroll
+        for (int c = 0; c < 2; c++) S[c][j] = (MODE != 1 && d < D && v_ok[c]) ? from[(size_t)d * V + vc[c]] : 0.f;
+        if (MODE == 1) P[j] = 1.f;
     }
     const T* proj = (const T*)a.proj;
+    // a tile's q, k, decay and v travel through registers: the next tile's loads are in flight while this one is computed
+    float rq[PER], rk[PER], rd[PER], rv[2];
+    auto fetch = [&](int t0) {
+        const int nt = min(GLA_TT, s1 - t0);
+#pragma unroll
+        for (int u = 0; u < PER; u++) {
+            const int i = threadIdx.x + u * GLA_WARPS * 32;
+            const int tt = i / DP, d = i % DP;
+            rq[u] = 0.f; rk[u] = 0.f; rd[u] = 1.f;
+            if (i < GLA_TT * DP && tt < nt && d < D) {
+                const T* row = proj + (size_t)(t0 + tt) * a.proj_stride;
+                if (MODE != 1) rq[u] = to_f<T>(row[h * D + d]) * a.q_scale;
+                rk[u] = to_f<T>(row[HD + h * D + d]);
+                rd[u] = a.decay[(size_t)(t0 + tt) * HD + h * D + d];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; u++) {                  // 8 tokens x 64 channels = 2 per thread
+            const int i = threadIdx.x + u * GLA_WARPS * 32;
+            const int tt = i / GLA_VT, c = v0 + i % GLA_VT;
+            rv[u] = (tt < nt && c < V) ? to_f<T>(proj[(size_t)(t0 + tt) * a.proj_stride + 2 * HD + h * V + c]) : 0.f;
+        }
+    };
+    auto stash = [&]() {
+#pragma unroll
+        for (int u = 0; u < PER; u++) {
+            const int i = threadIdx.x + u * GLA_WARPS * 32;
+            if (i < GLA_TT * DP) { (&q_s[0][0])[i] = rq[u]; (&k_s[0][0])[i] = rk[u]; (&d_s[0][0])[i] = rd[u]; }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; u++) (&v_s[0][0])[threadIdx.x + u * GLA_WARPS * 32] = rv[u];
+    };
+    if (s0 < s1) { fetch(s0); stash(); }
+    __syncthreads();
     for (int t0 = s0; t0 < s1; t0 += GLA_TT) {
         const int nt = min(GLA_TT, s1 - t0);
-        for (int i = threadIdx.x; i < GLA_TT * DP; i += blockDim.x) {
-            const int tt = i / DP, d = i % DP;
-            float q = 0.f, k = 0.f, dec = 1.f;
-            if (tt < nt && d < D) {
-                const T* row = proj + (size_t)(t0 + tt) * a.proj_stride;
-                q = to_f<T>(row[h * D + d]) * a.q_scale;
-                k = to_f<T>(row[HD + h * D + d]);
-                dec = a.decay[(size_t)(t0 + tt) * HD + h * D + d];
-            }
-            q_s[tt][d] = q; k_s[tt][d] = k; d_s[tt][d] = dec;
-        }
-        {
-            const int tt = threadIdx.x >> 5;           // 8 warps = 8 tokens of the tile
-            v_s[tt][lane] = (tt < nt && v_ok) ? to_f<T>(proj[(size_t)(t0 + tt) * a.proj_stride + 2 * HD + h * V + vch]) : 0.f;
-        }
-        __syncthreads();
+        const bool more = t0 + GLA_TT < s1;
+        if (more) fetch(t0 + GLA_TT);
         for (int tt = 0; tt < nt; tt++) {
-            const float vv = v_s[tt][lane];
-            float acc = 0.f;
+            const float va = v_s[tt][lane], vb = v_s[tt][lane + 32];
+            float acc_a = 0.f, acc_b = 0.f;
+            if constexpr (DPT % 4 == 0) {
+                const float4* d4 = reinterpret_cast<const float4*>(&d_s[tt][warp * DPT]);
+                const float4* k4 = reinterpret_cast<const float4*>(&k_s[tt][warp * DPT]);
+                const float4* q4 = reinterpret_cast<const float4*>(&q_s[tt][warp * DPT]);
 #pragma unroll
-            for (int j = 0; j < DPT; j++) {
-                const int d = warp * DPT + j;
-                S[j] = fmaf(d_s[tt][d], S[j], k_s[tt][d] * vv);
-                if (MODE == 1) P[j] *= d_s[tt][d];
-                else acc = fmaf(S[j], q_s[tt][d], acc);
+                for (int j4 = 0; j4 < DPT / 4; j4++) {
+                    const float4 dd = d4[j4], kk = k4[j4];
+                    const float dv[4] = {dd.x, dd.y, dd.z, dd.w}, kv[4] = {kk.x, kk.y, kk.z, kk.w};
+                    float qv[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (MODE != 1) { const float4 qq = q4[j4]; qv[0] = qq.x; qv[1] = qq.y; qv[2] = qq.z; qv[3] = qq.w; }
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int j = j4 * 4 + e;
+                        S[0][j] = fmaf(dv[e], S[0][j], kv[e] * va);
+                        S[1][j] = fmaf(dv[e], S[1][j], kv[e] * vb);
+                        if (MODE == 1) P[j] *= dv[e];
+                        else { acc_a = fmaf(S[0][j], qv[e], acc_a); acc_b = fmaf(S[1][j], qv[e], acc_b); }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < DPT; j++) {
+                    const int d = warp * DPT + j;
+                    const float dec = d_s[tt][d], kk = k_s[tt][d];
+                    S[0][j] = fmaf(dec, S[0][j], kk * va);
+                    S[1][j] = fmaf(dec, S[1][j], kk * vb);
+                    if (MODE == 1) P[j] *= dec;
+                    else { acc_a = fmaf(S[0][j], q_s[tt][d], acc_a); acc_b = fmaf(S[1][j], q_s[tt][d], acc_b); }
+                }
             }
-            if (MODE != 1) part_s[tt][warp][lane] = acc;
+            if (MODE != 1) { part_s[tt][warp][lane] = acc_a; part_s[tt][warp][lane + 32] = acc_b; }
         }
-        __syncthreads();
+        __syncthreads();                               // every warp is done with the tile; the partial outputs are complete
         if (MODE != 1) {
-            const int tt = warp;
-            if (tt < nt && v_ok) {
-                float o = 0.f;
+            const int tt = warp;                       // 8 warps = the tile's 8 tokens
+            if (tt < nt) {
 #pragma unroll
-                for (int w = 0; w < GLA_WARPS; w++) o += part_s[tt][w][lane];
-                a.y[(size_t)(t0 + tt) * HV + h * V + vch] = o;
+                for (int c = 0; c < 2; c++) {
+                    float o = 0.f;
+#pragma unroll
+                    for (int w = 0; w < GLA_WARPS; w++) o += part_s[tt][w][lane + 32 * c];
+                    if (v_ok[c]) a.y[(size_t)(t0 + tt) * HV + h * V + vc[c]] = o;
+                }
             }
         }
-        // the next tile's staging writes q_s..v_s, which nobody reads any more; part_s is written again only
-        // after the next barrier
+        if (more) stash();
+        __syncthreads();                               // the next tile is in shared memory; the partial outputs are free again
     }
     if (MODE == 2 && s1 != seq_end) return;            // only the chunk that holds the sequence's end leaves its state
     if (MODE == 2 && s0 == s1 && chunk != 0) return;   // (an empty chunk after the end: the one before it did)
@@ -148,7 +215,9 @@ __global__ void __launch_bounds__(GLA_WARPS * 32) gla_scan_kernel(GlaArgs a) {
     for (int j = 0; j < DPT; j++) {
         const int d = warp * DPT + j;
         float* to = MODE == 1 ? cst : st;
-        if (d < D && v_ok) to[(size_t)d * V + vch] = S[j];
+#pragma unroll
+        for (int c = 0; c < 2; c++)
+            if (d < D && v_ok[c]) to[(size_t)d * V + vc[c]] = S[c][j];
         if (MODE == 1 && d < D && blockIdx.x == 0 && lane == 0)
             a.chunk_decay[((size_t)b * a.n_chunks + chunk) * a.heads * D + (size_t)h * D + d] = P[j];
     }
@@ -206,8 +275,10 @@ static int check(const GlaArgs& a) {
 extern "C" int tb_gla_decay(const GlaArgs* args, cudaStream_t stream) {
     if (args->n_tokens <= 0) return 0;
     if (check(*args)) return -1;
-    if (args->rank > 4096) return tb_refuse("gla: rank %d", args->rank);
-    tb_launch(gla_decay_kernel, dim3(args->n_tokens), dim3(256), (size_t)args->rank * sizeof(float), stream, *args);
+    if (args->rank > 256) return tb_refuse("gla: a decay of rank %d; the kernel takes up to 256", args->rank);
+    const int HD = args->heads * args->D;
+    tb_launch(gla_decay_kernel, dim3((args->n_tokens + GLA_DECAY_TOK - 1) / GLA_DECAY_TOK, (HD + 255) / 256), dim3(256),
+              (size_t)GLA_DECAY_TOK * args->rank * sizeof(float), stream, *args);
     return tb_launch_status();
 }
 
@@ -220,7 +291,7 @@ extern "C" int tb_gla_scan(const GlaArgs* args, int dtype, cudaStream_t stream) 
     const bool chunks = a.n_chunks > 1;
     if (chunks && (a.chunk_len <= 0 || a.chunk_state == nullptr || a.chunk_decay == nullptr || (long long)a.batch * a.n_chunks > 65535))
         return tb_refuse("gla: %d chunks of %d tokens need their scratch (and batch x chunks <= 65535)", a.n_chunks, a.chunk_len);
-    dim3 grid((a.V + 31) / 32, a.heads, chunks ? a.batch * a.n_chunks : a.batch);
+    dim3 grid((a.V + GLA_VT - 1) / GLA_VT, a.heads, chunks ? a.batch * a.n_chunks : a.batch);
 #define GLA_SCAN_M(N, M) TB_DISPATCH_1(dtype, T, tb_launch(gla_scan_kernel<T, N, M>, dim3(grid), dim3(GLA_WARPS * 32), 0, stream, a))
 #define GLA_SCAN(N) do { if (mode == 0) GLA_SCAN_M(N, 0); else if (mode == 1) GLA_SCAN_M(N, 1); else GLA_SCAN_M(N, 2); } while (0)
     for (int pass = 0; pass < (chunks ? 3 : 1); pass++) {
@@ -244,10 +315,11 @@ extern "C" int tb_gla_scan(const GlaArgs* args, int dtype, cudaStream_t stream) 
     return 0;
 }
 
-// How a step of whole prompts is cut in time: chunks of at least 64 tokens, as many as give every SM about two CTAs.
+// How a step of whole prompts is cut in time: chunks of at least 64 tokens, as many as fill the GPU once (two CTAs an SM)
+// and no more, so that no CTA waits for a second round.
 extern "C" int tb_gla_plan(int heads, int V, int batch, int max_seq_len, int sms, int* chunk_len) {
-    const long long ctas = (long long)((V + 31) / 32) * heads * batch;
-    int want = (int)((2LL * sms + ctas - 1) / ctas);
+    const long long ctas = (long long)((V + GLA_VT - 1) / GLA_VT) * heads * batch;
+    int want = (int)((2LL * sms) / ctas);
     int most = max_seq_len / 64;
     if (want > most) want = most;
     if (want <= 1) { *chunk_len = 0; return 1; }

@@ -1,6 +1,7 @@
 // A feed-forward made of experts behind a router.
 //
-//   tb_moe_route     per token: logits z = R x (32-bit sums), scores s = sigmoid(z); choice scores s + correction;
+//   tb_moe_route     per token, from the logits z = R x (32-bit sums of a product, given as split-K partial sums):
+//                    scores s = sigmoid(z); choice scores s + correction;
 //                    experts form `groups` equal groups of neighbours, a group's score is the sum of its
 //                    `group_top` largest choice scores, experts outside the `keep` best groups cannot be chosen
 //                    (their choice scores count as minus infinity); the `top` largest choice scores win (the
@@ -17,10 +18,9 @@
 TB_EXPORT_ERROR()
 
 struct MoeRouteArgs {
-    const void* x; long long x_stride;         // [T][W]
-    const void* router;                        // [E][W]
+    const float* logits; int splits; long long split_stride, row_stride;   // [splits][T][>= E (+ 1)]: 32-bit partial sums of R x
     const float* correction;                   // [E] or null
-    const void* shared_gate;                   // [W] or null
+    int has_gate;                              // column E of the logits is the shared expert's gate g . x
     int* idx; float* weight;                   // [T][top]
     float* gate;                               // [T] (if shared_gate)
     int n_tokens, W, E, top, groups, keep, group_top;
@@ -36,7 +36,6 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
     }
 }
 
-template <typename T, typename TW>
 __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteArgs a) {
     pdl_launch_dependents();
     extern __shared__ float smem[];
@@ -47,18 +46,12 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteArgs a) {
     float* gscore = choice + a.E;
     pdl_wait();
     if (t >= a.n_tokens) return;
-    const T* x = (const T*)a.x + (size_t)t * a.x_stride;
-    for (int e = 0; e <= a.E; e++) {
-        if (e == a.E && a.shared_gate == nullptr) break;
-        const TW* w = (e < a.E) ? (const TW*)a.router + (size_t)e * a.W : (const TW*)a.shared_gate;
+    for (int e = lane; e < a.E + (a.has_gate ? 1 : 0); e += 32) {
         float d = 0.f;
-        for (int c = lane; c < a.W; c += 32) d = fmaf(to_f<T>(x[c]), to_f<TW>(w[c]), d);
-        d = warp_sum(d);
-        if (lane == 0) {
-            const float s = 1.f / (1.f + expf(-d));
-            if (e < a.E) { score[e] = s; choice[e] = s + (a.correction ? a.correction[e] : 0.f); }
-            else a.gate[t] = s;
-        }
+        for (int sp = 0; sp < a.splits; sp++) d += a.logits[(size_t)sp * a.split_stride + (size_t)t * a.row_stride + e];
+        const float s = 1.f / (1.f + expf(-d));
+        if (e < a.E) { score[e] = s; choice[e] = s + (a.correction ? a.correction[e] : 0.f); }
+        else a.gate[t] = s;
     }
     __syncwarp();
     if (a.groups > 1) {
@@ -179,7 +172,7 @@ __global__ void __launch_bounds__(256) moe_down_kernel(MoeExpertArgs a) {
 
 // ---------------------------------------------------------------------------
 // Many tokens (bfloat16): the (token, expert) pairs are grouped by expert on the device and every expert's
-// pairs go through tensor-core products in tiles of 64 pairs, so that an expert's matrices are read once
+// pairs go through tensor-core products in tiles of 128 pairs, so that an expert's matrices are read once
 // per tile of pairs and not once per pair.  Nothing here depends on values the host knows: the grid is
 // sized for the most tiles there can be and the surplus CTAs leave at once.
 //
@@ -187,7 +180,8 @@ __global__ void __launch_bounds__(256) moe_down_kernel(MoeExpertArgs a) {
 //   tb_moe_grouped   act = silu(G_e x) * (U_e x) per pair (one launch), pair outputs D_e act times the pair's
 //                    weight in 32-bit (one launch), and their sum per token with the shared expert (one launch)
 // ---------------------------------------------------------------------------
-constexpr int MG_BM = 64, MG_BN = 128, MG_BK = 32, MG_PITCH = MG_BK * 2 + 16;
+constexpr int MG_BM = 128, MG_BN = 128, MG_BK = 64, MG_PITCH = MG_BK * 2 + 16, MG_STAGES = 3, MG_THREADS = 256;
+constexpr int MG_STAGE_BYTES = (MG_BM + MG_BN) * MG_PITCH;
 
 struct MoeGroupArgs {
     const int* idx;            // [P] expert of every pair (P = tokens * top)
@@ -257,95 +251,107 @@ struct MoeGroupedArgs {
 
 // GATED: rows of x (by pair / top) times [G_e ; U_e] for 64 columns of ff, then silu(g) * u  ->  act[pair]
 // else:  rows of act (by pair) times D_e for 128 columns of W, times the pair's weight          ->  pair_out[pair]
+// A tile is 128 pairs x 128 weight rows, eight warps (4 x 2) of 32 x 64 each, k in blocks of 64 through a three-stage
+// cp.async ring.  GATED lays the weight rows out so that a warp holds a gate column and its up column in one thread:
+// rows 64w .. 64w+31 of the tile are gate rows n0 + 32w .., rows 64w+32 .. 64w+63 the up rows of the same columns.
 template <bool GATED>
-__global__ void __launch_bounds__(128) moe_grouped_kernel(MoeGroupedArgs a) {
+__global__ void __launch_bounds__(MG_THREADS, 2) moe_grouped_kernel(MoeGroupedArgs a) {
     pdl_launch_dependents();
-    __shared__ __align__(16) unsigned char smem[2 * (MG_BM + MG_BN) * MG_PITCH];
+    extern __shared__ __align__(16) unsigned char mg_ring[];
     __shared__ int row_src[MG_BM];
     const int tile = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wm = warp >> 1, wn = warp & 1;
     pdl_wait();
     if (tile >= *a.n_tiles) return;
     const int e = a.tile_expert[tile], row0 = a.tile_row0[tile], rows = a.tile_rows[tile];
     const int K = GATED ? a.W : a.ff;
     const int N = GATED ? a.ff : a.W;
     const int n0 = blockIdx.y * (GATED ? MG_BN / 2 : MG_BN);
-    if (threadIdx.x < MG_BM) {
-        const int p = threadIdx.x < rows ? a.perm[row0 + threadIdx.x] : -1;
-        row_src[threadIdx.x] = p;
-    }
+    if (threadIdx.x < MG_BM) row_src[threadIdx.x] = threadIdx.x < rows ? a.perm[row0 + threadIdx.x] : -1;
     __syncthreads();
     const bf16* A = GATED ? a.x : a.act;
     const long long a_stride = GATED ? a.x_stride : a.ff;
     const bf16* B0 = GATED ? a.gate_w + (size_t)e * a.ff * a.W : a.down_w + (size_t)e * a.W * a.ff;
     const bf16* B1 = a.up_w + (size_t)e * a.ff * a.W;
-    auto stage_a = [&](int s) { return smem + (size_t)s * (MG_BM + MG_BN) * MG_PITCH; };
-    auto stage_b = [&](int s) { return stage_a(s) + MG_BM * MG_PITCH; };
     auto load = [&](int s, int k0) {
-        unsigned char* sa = stage_a(s); unsigned char* sb = stage_b(s);
-        for (int c = threadIdx.x; c < MG_BM * 4; c += 128) {
-            const int r = c >> 2, ch = c & 3, k = k0 + ch * 8;
+        unsigned char* sa = mg_ring + (size_t)s * MG_STAGE_BYTES; unsigned char* sb = sa + MG_BM * MG_PITCH;
+        for (int c = threadIdx.x; c < MG_BM * (MG_BK / 8); c += MG_THREADS) {
+            const int r = c >> 3, ch = c & 7, k = k0 + ch * 8;
             const int p = row_src[r];
             const bool ok = p >= 0 && k < K;
             const bf16* src = A + (size_t)(ok ? (GATED ? p / a.top : p) : 0) * a_stride + (ok ? k : 0);
             mg_cp16(sa + r * MG_PITCH + ch * 16, src, ok);
         }
-        for (int c = threadIdx.x; c < MG_BN * 4; c += 128) {
-            const int r = c >> 2, ch = c & 3, k = k0 + ch * 8;
+        for (int c = threadIdx.x; c < MG_BN * (MG_BK / 8); c += MG_THREADS) {
+            const int r = c >> 3, ch = c & 7, k = k0 + ch * 8;
             int n; const bf16* base;
-            if (GATED) { n = n0 + (r & 63); base = (r < 64) ? B0 : B1; } else { n = n0 + r; base = B0; }
+            if (GATED) { n = n0 + (r >> 6) * 32 + (r & 31); base = (r & 32) ? B1 : B0; } else { n = n0 + r; base = B0; }
             const bool ok = n < N && k < K;
             mg_cp16(sb + r * MG_PITCH + ch * 16, base + (size_t)(ok ? n : 0) * K + (ok ? k : 0), ok);
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    float acc[MG_BN / 8][4];
+    float acc[2][8][4];
 #pragma unroll
-    for (int n = 0; n < MG_BN / 8; n++) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
+    for (int m = 0; m < 2; m++)
+#pragma unroll
+        for (int n = 0; n < 8; n++) { acc[m][n][0] = acc[m][n][1] = acc[m][n][2] = acc[m][n][3] = 0.f; }
     const int nk = (K + MG_BK - 1) / MG_BK;
-    load(0, 0);
+#pragma unroll
+    for (int s = 0; s < MG_STAGES - 1; s++) {
+        if (s < nk) load(s, s * MG_BK);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     for (int kb = 0; kb < nk; kb++) {
-        if (kb + 1 < nk) { load((kb + 1) & 1, (kb + 1) * MG_BK); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
-        else asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();
-        const unsigned char* sa = stage_a(kb & 1); const unsigned char* sb = stage_b(kb & 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(MG_STAGES - 2) : "memory");
+        __syncthreads();                               // block kb has landed; everybody is done with block kb - 1
+        if (kb + MG_STAGES - 1 < nk) load((kb + MG_STAGES - 1) % MG_STAGES, (kb + MG_STAGES - 1) * MG_BK);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const unsigned char* sa = mg_ring + (size_t)(kb % MG_STAGES) * MG_STAGE_BYTES; const unsigned char* sb = sa + MG_BM * MG_PITCH;
 #pragma unroll
         for (int ks = 0; ks < MG_BK / 16; ks++) {
-            uint32_t fa[4];
-            mg_ldsm(mg_smem(sa + (warp * 16 + (lane & 15)) * MG_PITCH + (ks * 16 + (lane >> 4) * 8) * 2), fa[0], fa[1], fa[2], fa[3]);
+            uint32_t fa[2][4];
 #pragma unroll
-            for (int n = 0; n < MG_BN / 8; n += 2) {
+            for (int m = 0; m < 2; m++)
+                mg_ldsm(mg_smem(sa + (wm * 32 + m * 16 + (lane & 15)) * MG_PITCH + (ks * 16 + (lane >> 4) * 8) * 2),
+                        fa[m][0], fa[m][1], fa[m][2], fa[m][3]);
+#pragma unroll
+            for (int n = 0; n < 8; n += 2) {
                 uint32_t b0, b1, b2, b3;
-                mg_ldsm(mg_smem(sb + (n * 8 + (lane >> 4) * 8 + (lane & 7)) * MG_PITCH + (ks * 16 + ((lane >> 3) & 1) * 8) * 2), b0, b1, b2, b3);
-                mg_mma(acc[n], fa, b0, b1);
-                mg_mma(acc[n + 1], fa, b2, b3);
+                mg_ldsm(mg_smem(sb + (wn * 64 + n * 8 + (lane >> 4) * 8 + (lane & 7)) * MG_PITCH + (ks * 16 + ((lane >> 3) & 1) * 8) * 2), b0, b1, b2, b3);
+#pragma unroll
+                for (int m = 0; m < 2; m++) { mg_mma(acc[m][n], fa[m], b0, b1); mg_mma(acc[m][n + 1], fa[m], b2, b3); }
             }
         }
-        __syncthreads();                              // the load after next overwrites this stage
     }
-    const int ra = warp * 16 + (lane >> 2), rb = ra + 8, cq = (lane & 3) * 2;
-    const int pa = row_src[ra], pb = row_src[rb];
-    if (GATED) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    const int cq = (lane & 3) * 2;
 #pragma unroll
-        for (int n = 0; n < MG_BN / 16; n++) {
+    for (int m = 0; m < 2; m++) {
+        const int ra = wm * 32 + m * 16 + (lane >> 2), rb = ra + 8;
+        const int pa = row_src[ra], pb = row_src[rb];
+        if (GATED) {
 #pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const int col = n0 + n * 8 + cq + j;
-                if (col >= N) continue;
-                const float ga = acc[n][j], ua = acc[n + MG_BN / 16][j], gb = acc[n][2 + j], ub = acc[n + MG_BN / 16][2 + j];
-                if (pa >= 0) a.act[(size_t)pa * a.ff + col] = __float2bfloat16_rn(ga / (1.f + expf(-ga)) * ua);
-                if (pb >= 0) a.act[(size_t)pb * a.ff + col] = __float2bfloat16_rn(gb / (1.f + expf(-gb)) * ub);
+            for (int n = 0; n < 4; n++) {
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const int col = n0 + wn * 32 + n * 8 + cq + j;
+                    if (col >= N) continue;
+                    const float ga = acc[m][n][j], ua = acc[m][n + 4][j], gb = acc[m][n][2 + j], ub = acc[m][n + 4][2 + j];
+                    if (pa >= 0) a.act[(size_t)pa * a.ff + col] = __float2bfloat16_rn(ga / (1.f + expf(-ga)) * ua);
+                    if (pb >= 0) a.act[(size_t)pb * a.ff + col] = __float2bfloat16_rn(gb / (1.f + expf(-gb)) * ub);
+                }
             }
-        }
-    } else {
-        const float wa = pa >= 0 ? a.weight[pa] : 0.f, wb = pb >= 0 ? a.weight[pb] : 0.f;
+        } else {
+            const float wa = pa >= 0 ? a.weight[pa] : 0.f, wb = pb >= 0 ? a.weight[pb] : 0.f;
 #pragma unroll
-        for (int n = 0; n < MG_BN / 8; n++) {
+            for (int n = 0; n < 8; n++) {
 #pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const int col = n0 + n * 8 + cq + j;
-                if (col >= N) continue;
-                if (pa >= 0) a.pair_out[(size_t)pa * a.W + col] = acc[n][j] * wa;
-                if (pb >= 0) a.pair_out[(size_t)pb * a.W + col] = acc[n][2 + j] * wb;
+                for (int j = 0; j < 2; j++) {
+                    const int col = n0 + wn * 64 + n * 8 + cq + j;
+                    if (col >= N) continue;
+                    if (pa >= 0) a.pair_out[(size_t)pa * a.W + col] = acc[m][n][j] * wa;
+                    if (pb >= 0) a.pair_out[(size_t)pb * a.W + col] = acc[m][n][2 + j] * wb;
+                }
             }
         }
     }
@@ -383,10 +389,18 @@ extern "C" int tb_moe_grouped(const MoeGroupedArgs* args, const float* shared, i
     if (n_tokens <= 0) return 0;
     if (a.W % 8 || a.ff % 8 || ((uintptr_t)a.x & 15) || (a.x_stride % 8))
         return tb_refuse("moe_grouped: W=%d and ff=%d must be multiples of 8 and the rows 16-byte aligned", a.W, a.ff);
-    tb_launch(moe_grouped_kernel<true>, dim3(max_tiles, (a.ff + 63) / 64), dim3(128), 0, stream, a);
+    constexpr int SMEM = MG_STAGES * MG_STAGE_BYTES;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e1 = cudaFuncSetAttribute(moe_grouped_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e2 = cudaFuncSetAttribute(moe_grouped_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e1 != cudaSuccess || e2 != cudaSuccess) return (int)(e1 != cudaSuccess ? e1 : e2);
+        attr_set = true;
+    }
+    tb_launch(moe_grouped_kernel<true>, dim3(max_tiles, (a.ff + 63) / 64), dim3(MG_THREADS), SMEM, stream, a);
     int st = tb_launch_status();
     if (st) return st;
-    tb_launch(moe_grouped_kernel<false>, dim3(max_tiles, (a.W + MG_BN - 1) / MG_BN), dim3(128), 0, stream, a);
+    tb_launch(moe_grouped_kernel<false>, dim3(max_tiles, (a.W + MG_BN - 1) / MG_BN), dim3(MG_THREADS), SMEM, stream, a);
     st = tb_launch_status();
     if (st) return st;
     const long long n = (long long)n_tokens * a.W;
@@ -395,7 +409,7 @@ extern "C" int tb_moe_grouped(const MoeGroupedArgs* args, const float* shared, i
     return tb_launch_status();
 }
 
-extern "C" int tb_moe_route(const MoeRouteArgs* args, int x_dtype, int w_dtype, cudaStream_t stream) {
+extern "C" int tb_moe_route(const MoeRouteArgs* args, cudaStream_t stream) {
     const MoeRouteArgs& a = *args;
     if (a.n_tokens <= 0) return 0;
     if (a.E <= 0 || a.top < 1 || a.top > a.E || a.groups < 1 || a.E % a.groups || a.keep < 1 || a.keep > a.groups ||
@@ -404,8 +418,7 @@ extern "C" int tb_moe_route(const MoeRouteArgs* args, int x_dtype, int w_dtype, 
     const int warps = 4;
     const size_t smem = (size_t)warps * (2 * a.E + a.groups) * sizeof(float);
     if (smem > 48 * 1024) return tb_refuse("moe_route: %d experts are more than one block holds", a.E);
-    TB_DISPATCH_1(x_dtype, T, TB_DISPATCH_1(w_dtype, TW,
-        tb_launch(moe_route_kernel<T, TW>, dim3((a.n_tokens + warps - 1) / warps), dim3(warps * 32), smem, stream, a)));
+    tb_launch(moe_route_kernel, dim3((a.n_tokens + warps - 1) / warps), dim3(warps * 32), smem, stream, a);
     return tb_launch_status();
 }
 

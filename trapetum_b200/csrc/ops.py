@@ -1291,25 +1291,34 @@ def latent_decode(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor,
         raise KernelError(f"latent_decode: q {tuple(q.shape)} does not fit {heads} heads of {C + R}")
     if sink is not None and (sink.dtype != torch.float32 or sink.numel() != heads or not sink.is_contiguous()):
         raise KernelError(f"latent_decode: the sink must be contiguous float32 [{heads}]")
-    pieces = max(1, min((len_bucket + 255) // 256, max(1, (2 * sm_count(q.device)) // max(1, B * heads))))
+    lib = build.load("attention_latent")
+    mma = q.dtype == torch.bfloat16 and bool(lib.tb_latent_decode_mma_takes(c_int(C), c_int(R))) and q.stride(0) % 8 == 0 \
+        and q.data_ptr() % 16 == 0
+    # pieces: enough CTAs for about two per SM, none shorter than 128 keys (256 on the generic kernel)
+    units = B * ((heads + 15) // 16) if mma else B * heads
+    shortest = 128 if mma else 256
+    pieces = max(1, min((len_bucket + shortest - 1) // shortest, max(1, (2 * sm_count(q.device)) // max(1, units))))
     out = torch.empty((B, heads * C), dtype=q.dtype, device=q.device)
-    scratch = torch.empty(B * heads * pieces * (C + 2), dtype=torch.float32, device=q.device) if pieces > 1 else None
+    scratch = torch.empty(B * heads * pieces * (C + 2), dtype=torch.float32, device=q.device) if (pieces > 1 or mma) else None
     a = _LatentDecodeArgs()
     a.q = q.data_ptr(); a.q_stride = q.stride(0); a.pool = pool.data_ptr()
     a.page_table = page_table.data_ptr(); a.pt_stride = page_table.stride(0); a.page_rows = PAGE_ROWS
     a.len_after = len_after.data_ptr(); a.sink = sink.data_ptr() if sink is not None else None
     a.out = out.data_ptr(); a.out_stride = out.stride(0); a.partial = scratch.data_ptr() if scratch is not None else None
     a.heads = heads; a.C = C; a.R = R; a.out_dim = C; a.n_splits = pieces; a.scale = scale
-    lib = build.load("attention_latent")
-    _check(lib, lib.tb_latent_decode(ctypes.byref(a), c_int(code(q.dtype)), c_int(B), _stream()), "latent_decode",
-           2 if pieces > 1 else 1)
+    if mma:
+        _check(lib, lib.tb_latent_decode_mma(ctypes.byref(a), c_int(B), _stream()), "latent_decode_mma", 2)
+    else:
+        _check(lib, lib.tb_latent_decode(ctypes.byref(a), c_int(code(q.dtype)), c_int(B), _stream()), "latent_decode",
+               2 if pieces > 1 else 1)
     return out
 
 
-def attn_prefill_sink(q, k, v, seq_start, token_seq, n_heads, head_dim, scale, sink, max_seq_len) -> torch.Tensor:
+def attn_prefill_sink(q, k, v, seq_start, token_seq, n_heads, head_dim, scale, sink, max_seq_len, seq_lens=None) -> torch.Tensor:
     """Causal prefill attention of packed sequences, one kv head per query head, whose softmax denominators also
-    hold ``exp(sink[h])`` (``sink`` float32 [n_heads], or None).  bfloat16 with a head size the tensor-core kernel
-    takes runs there, everything else on the generic kernel."""
+    hold ``exp(sink[h])`` (``sink`` float32 [n_heads], or None).  bfloat16 runs on the tcgen05 kernel (head sizes 64, 128,
+    256, with the sequences' lengths on the host in ``seq_lens``) or the mma.sync kernel (other multiples of 16),
+    everything else on the generic kernel."""
     _cuda(q, k, v, seq_start, token_seq, sink)
     for name, t in (("q", q), ("k", k), ("v", v)):
         _rows_contig(t, "attention: " + name)
@@ -1320,6 +1329,14 @@ def attn_prefill_sink(q, k, v, seq_start, token_seq, n_heads, head_dim, scale, s
     T = q.shape[0]
     out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
     aligned = all(t.data_ptr() % 16 == 0 and t.stride(0) % 8 == 0 for t in (q, k, v))
+    if attn_prefill_tc_takes(q.dtype, head_dim) and aligned and seq_lens is not None:
+        lib = build.load(attn_prefill_tc_lib(head_dim))
+        B = len(seq_lens)
+        _check(lib, lib.tb_attn_prefill_tc_ex(_ptr(q), _ptr(k), _ptr(v), c_longlong(q.stride(0)), c_longlong(k.stride(0)),
+                                              _ptr(seq_start), _ptr(out), c_int(T), c_int(B), c_int(max(seq_lens)),
+                                              c_int(n_heads), c_int(n_heads), c_int(head_dim), c_float(scale), c_float(0.0),
+                                              c_int(0), _ptr(sink), _stream()), "attn_prefill_tc", 2)
+        return out
     if attn_prefill_takes(q.dtype, head_dim) and aligned:
         lib = build.load(attn_prefill_lib(head_dim))
         B = seq_start.numel() - 1
@@ -1340,38 +1357,39 @@ def attn_prefill_sink(q, k, v, seq_start, token_seq, n_heads, head_dim, scale, s
 # Experts behind a router
 # ---------------------------------------------------------------------------
 class _MoeRouteArgs(ctypes.Structure):
-    _fields_ = [("x", c_void_p), ("x_stride", c_longlong), ("router", c_void_p), ("correction", c_void_p),
-                ("shared_gate", c_void_p), ("idx", c_void_p), ("weight", c_void_p), ("gate", c_void_p),
+    _fields_ = [("logits", c_void_p), ("splits", c_int), ("split_stride", c_longlong), ("row_stride", c_longlong),
+                ("correction", c_void_p), ("has_gate", c_int), ("idx", c_void_p), ("weight", c_void_p), ("gate", c_void_p),
                 ("n_tokens", c_int), ("W", c_int), ("E", c_int), ("top", c_int), ("groups", c_int), ("keep", c_int),
                 ("group_top", c_int), ("weight_eps", c_float)]
 
 
-def moe_route(x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], shared_gate: Optional[torch.Tensor],
+def moe_route(logits: torch.Tensor, experts: int, correction: Optional[torch.Tensor], has_gate: bool,
               top: int, groups: int, keep: int, group_top: int, weight_eps: float):
-    """Sigmoid-scored routing with groups (see moe.cu).  Returns (chosen experts int32 [T, top], their weights float32
-    [T, top], the shared expert's gate float32 [T] or None)."""
-    _cuda(x, router, correction, shared_gate)
-    _rows_contig(x, "moe_route: x")
-    T, W = x.shape
-    E = router.shape[0]
-    if router.dim() != 2 or router.shape[1] != W or not router.is_contiguous():
-        raise KernelError(f"moe_route: the router must be contiguous [experts, {W}]")
+    """Sigmoid-scored routing with groups (see moe.cu) from the router's logits: float32 [T, >= experts (+ 1)] or
+    partial sums [splits, T, ...] of the router product (column ``experts`` is the shared expert's gate product if
+    ``has_gate``).  Returns (chosen experts int32 [T, top], their weights float32 [T, top], the shared expert's gate
+    float32 [T] or None)."""
+    _cuda(logits, correction)
+    if logits.dim() == 2:
+        logits = logits[None]
+    E = experts
+    T = logits.shape[1]
+    if logits.dtype != torch.float32 or logits.stride(2) != 1 or logits.shape[2] < E + int(has_gate):
+        raise KernelError(f"moe_route: logits must be float32 [splits, T, >= {E + int(has_gate)}], got {tuple(logits.shape)} {logits.dtype}")
     if correction is not None and (correction.dtype != torch.float32 or correction.numel() != E or not correction.is_contiguous()):
         raise KernelError(f"moe_route: the correction must be contiguous float32 [{E}]")
-    if shared_gate is not None and (shared_gate.dtype != router.dtype or shared_gate.numel() != W or not shared_gate.is_contiguous()):
-        raise KernelError(f"moe_route: the shared gate must be contiguous [{W}] of the router's dtype")
-    idx = torch.empty((T, top), dtype=torch.int32, device=x.device)
-    weight = torch.empty((T, top), dtype=torch.float32, device=x.device)
-    gate = torch.empty((T,), dtype=torch.float32, device=x.device) if shared_gate is not None else None
+    idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weight = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    gate = torch.empty((T,), dtype=torch.float32, device=logits.device) if has_gate else None
     a = _MoeRouteArgs()
-    a.x = x.data_ptr(); a.x_stride = x.stride(0); a.router = router.data_ptr()
+    a.logits = logits.data_ptr(); a.splits = logits.shape[0]; a.split_stride = logits.stride(0); a.row_stride = logits.stride(1)
     a.correction = correction.data_ptr() if correction is not None else None
-    a.shared_gate = shared_gate.data_ptr() if shared_gate is not None else None
+    a.has_gate = int(has_gate)
     a.idx = idx.data_ptr(); a.weight = weight.data_ptr(); a.gate = gate.data_ptr() if gate is not None else None
-    a.n_tokens = T; a.W = W; a.E = E; a.top = top; a.groups = groups; a.keep = keep; a.group_top = group_top
+    a.n_tokens = T; a.W = 0; a.E = E; a.top = top; a.groups = groups; a.keep = keep; a.group_top = group_top
     a.weight_eps = weight_eps
     lib = build.load("moe")
-    _check(lib, lib.tb_moe_route(ctypes.byref(a), c_int(code(x.dtype)), c_int(code(router.dtype)), _stream()), "moe_route")
+    _check(lib, lib.tb_moe_route(ctypes.byref(a), _stream()), "moe_route")
     return idx, weight, gate
 
 
@@ -1397,7 +1415,7 @@ def _moe_grouped(x, gate_w, up_w, down_w, idx, weight, shared, gate, out):
     E, ff = gate_w.shape[0], gate_w.shape[1]
     top = idx.shape[1]
     P = T * top
-    max_tiles = (P + 63) // 64 + min(E, P)
+    max_tiles = (P + 127) // 128 + min(E, P)          # tiles of 128 pairs; every expert may end with one that is not full
     ints = torch.empty(P + 3 * max_tiles + 1, dtype=torch.int32, device=x.device)
     perm, te, tr0, trn, nt = (ints[:P], ints[P:P + max_tiles], ints[P + max_tiles:P + 2 * max_tiles],
                               ints[P + 2 * max_tiles:P + 3 * max_tiles], ints[P + 3 * max_tiles:])

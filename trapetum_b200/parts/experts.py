@@ -25,6 +25,7 @@ from ..weights.loader import TensorSpec
 from .base import FeedForward, register_part
 from .feed_forward import GatedMLP
 from .linear import kernel_files as linear_kernels
+from .linear import linear_partials
 
 
 class RoutedExperts(FeedForward):
@@ -72,23 +73,30 @@ class RoutedExperts(FeedForward):
         return specs
 
     def bind(self, tensors) -> None:
-        self.w_router = tensors[self._name("router")]
+        router = tensors[self._name("router")]
         self.correction = tensors[self._name("correction")].float().contiguous() if self.params.get("correction") else None
         dt = tensors[self._expert(0, "gate")].dtype
         self.w_gate = torch.stack([tensors[self._expert(e, "gate")].to(dt) for e in range(self.E)]).contiguous()
         self.w_up = torch.stack([tensors[self._expert(e, "up")].to(dt) for e in range(self.E)]).contiguous()
         self.w_down = torch.stack([tensors[self._expert(e, "down")].to(dt) for e in range(self.E)]).contiguous()
-        self.w_shared_gate = None
+        rows = [router]
+        self.has_gate = False
         if self.shared is not None:
             self.shared.bind(tensors)
             if self.shared_gate_name:
-                self.w_shared_gate = tensors[self.prefix + self.shared_gate_name].to(self.w_router.dtype).reshape(-1).contiguous()
+                rows.append(tensors[self.prefix + self.shared_gate_name].to(router.dtype).reshape(1, -1))
+                self.has_gate = True
+        # one product gives the router's logits and the shared expert's gate; rows of zeros up to a multiple of 16
+        n = self.E + int(self.has_gate)
+        rows.append(torch.zeros((-n % 16, self.hidden), dtype=router.dtype, device=router.device))
+        self.w_router = torch.cat(rows, dim=0).contiguous()
 
     def kernel_files(self):
         return linear_kernels(self.rt.dtype) + ("moe", "activation")
 
     def forward(self, x, ctx):
-        idx, weight, gate = ops.moe_route(x, self.w_router, self.correction, self.w_shared_gate, self.top, self.groups,
+        logits = linear_partials(x, self.w_router)             # 32-bit sums; the routing itself is 32-bit throughout
+        idx, weight, gate = ops.moe_route(logits, self.E, self.correction, self.has_gate, self.top, self.groups,
                                           self.keep, self.group_top, self.weight_eps)
         shared = None
         if self.shared is not None:

@@ -62,6 +62,9 @@ class LatentAttention(Mixer):
         # the prefill kernels want one head size for q, k and v: the larger of the two, a multiple of 16; the
         # padding is zero columns of the matrices below, so it changes no sum
         self.hd = _round_up(max(self.D + self.R, self.V), 16)
+        if rt.dtype == torch.bfloat16:
+            # the tcgen05 kernel takes 64, 128 and 256: more padding, a faster kernel
+            self.hd = next((n for n in (64, 128, 256) if n >= self.hd), self.hd)
         self.has_sink = p.get("sink") is not None
         idx = torch.arange(0, self.rot_dims, 2, dtype=torch.float32)
         self._inv_freq_cpu = 1.0 / (torch.tensor(self.theta, dtype=torch.float32) ** (idx / max(self.rot_dims, 1)))
@@ -118,7 +121,9 @@ class LatentAttention(Mixer):
 
     def kernel_files(self):
         fast = ()
-        if ops.attn_prefill_takes(self.rt.dtype, self.hd):
+        if ops.attn_prefill_tc_takes(self.rt.dtype, self.hd):
+            fast = (ops.attn_prefill_tc_lib(self.hd),)
+        elif ops.attn_prefill_takes(self.rt.dtype, self.hd):
             fast = (ops.attn_prefill_lib(self.hd),)
         return linear_kernels(self.rt.dtype) + ("rope_kv", "attention_latent", "attention_simt") + fast
 
@@ -141,7 +146,7 @@ class LatentAttention(Mixer):
         if ctx.is_prefill:
             kv = linear(rows, self.w_up, dt)              # [T, 2 H hd]: every head's keys, then every head's values
             o = ops.attn_prefill_sink(q, kv[:, :H * hd], kv[:, H * hd:], ctx.seq_start, ctx.token_seq, H, hd, self.scale,
-                                      self.sink, ctx.max_seq_len)
+                                      self.sink, ctx.max_seq_len, ctx.seq_lens)
         else:
             ql = ops.head_linear(q, self.w_qmap, H)       # [B, H (C + R)]
             ol = ops.latent_decode(ql, line.k, line.page_table, ctx.len_after, self.sink, H, C, R, self.scale,
