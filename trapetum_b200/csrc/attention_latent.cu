@@ -29,27 +29,31 @@ struct LatentRowsArgs {
     void* rows;                                                // [T][C + R]
 };
 
+// A warp per token, four tokens per CTA: the row waits in the warp's piece of shared memory between the sum and the write.
 template <typename T>
 __global__ void __launch_bounds__(128) latent_rows_kernel(LatentRowsArgs a) {
     pdl_launch_dependents();
-    extern __shared__ float row_s[];
-    __shared__ float red[33];
-    const int t = blockIdx.x, W = a.C + a.R;
+    extern __shared__ float rows_s[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, W = a.C + a.R;
+    const int t = blockIdx.x * 4 + warp;
+    float* row_s = rows_s + (size_t)warp * W;
     pdl_wait();
+    if (t >= a.n_tokens) return;
     float sq = 0.f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    for (int c = lane; c < W; c += 32) {
         float v = 0.f;
         for (int s = 0; s < a.splits; s++) v += a.dkv[(size_t)s * a.split_stride + (size_t)t * W + c];
         row_s[c] = v;
         if (c < a.C) sq = fmaf(v, v, sq);
     }
-    const float rinv = 1.f / sqrtf(block_sum(sq, red) / (float)a.C + a.eps);     // its barriers also publish row_s
+    __syncwarp();
+    const float rinv = 1.f / sqrtf(warp_sum(sq) / (float)a.C + a.eps);
     const int pos = a.positions[t];
     const int page = a.page_table[(size_t)a.token_seq[t] * a.pt_stride + pos / a.page_rows];
     T* cache = (T*)a.pool + ((size_t)page * a.page_rows + pos % a.page_rows) * W;
     T* out = (T*)a.rows + (size_t)t * W;
     const int half = a.rot_dims / 2;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    for (int c = lane; c < W; c += 32) {
         float v;
         if (c < a.C) {
             v = row_s[c] * rinv * a.norm_w[c];
@@ -122,7 +126,7 @@ extern "C" int tb_latent_rows(const LatentRowsArgs* args, int dtype, cudaStream_
     if (a.n_tokens <= 0) return 0;
     if (a.C <= 0 || a.R < 0 || a.rot_dims < 0 || a.rot_dims % 2 || a.rot_dims > a.R || a.page_rows <= 0)
         return tb_refuse("latent_rows: C=%d R=%d rot_dims=%d page_rows=%d", a.C, a.R, a.rot_dims, a.page_rows);
-    TB_DISPATCH_1(dtype, T, tb_launch(latent_rows_kernel<T>, dim3(a.n_tokens), dim3(128), (size_t)(a.C + a.R) * sizeof(float), stream, a));
+    TB_DISPATCH_1(dtype, T, tb_launch(latent_rows_kernel<T>, dim3((a.n_tokens + 3) / 4), dim3(128), (size_t)4 * (a.C + a.R) * sizeof(float), stream, a));
     return tb_launch_status();
 }
 
@@ -256,7 +260,7 @@ __global__ void latent_combine_kernel(LatentDecodeArgs a) {
 // each), then O += P C with every warp taking a share of the latent's columns.  Partial (max, sum, o) go to the
 // scratch that latent_combine_kernel folds (it also adds the sink).
 // ---------------------------------------------------------------------------
-constexpr int LD_BN = 32, LD_HEADS = 16, LD_WARPS = 4;
+constexpr int LD_BN = 32;
 
 __device__ __forceinline__ uint32_t ld_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ld_cp16(void* dst, const void* src, bool valid) {
@@ -277,22 +281,25 @@ __device__ __forceinline__ void ld_mma(float* d, const uint32_t* a, uint32_t b0,
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// NP: pairs of 8-column tiles of the latent per warp (C <= NP * 64)
-template <int NP>
-__global__ void __launch_bounds__(LD_WARPS * 32) latent_decode_mma_kernel(LatentDecodeArgs a) {
+// MT: tiles of 16 heads per CTA (1 or 2), with 4 * MT warps.  NP: pairs of 8-column tiles of the latent per warp
+// (C <= NP * 16 * warps).  A warp scores 8 keys for 16 heads (four sums side by side, so that no product waits for the
+// one before it), takes the softmax of four heads, and adds its share of the latent's columns for all heads.
+template <int NP, int MT>
+__global__ void __launch_bounds__(MT * 128) latent_decode_mma_kernel(LatentDecodeArgs a) {
     pdl_launch_dependents();
+    constexpr int WARPS = 4 * MT, HEADS = 16 * MT, THREADS = WARPS * 32;
     extern __shared__ __align__(16) unsigned char sm[];
     const int KD = a.C + a.R, C = a.C;
     const int pitch = KD * 2 + 16;
-    unsigned char* q_s = sm;                                        // [16][pitch]
-    unsigned char* k_s = q_s + LD_HEADS * pitch;                    // [2][LD_BN][pitch]
-    float* s_s = (float*)(k_s + 2 * LD_BN * pitch);                 // [16][LD_BN]
-    unsigned char* p_s = (unsigned char*)(s_s + LD_HEADS * LD_BN);  // [16][LD_BN * 2 + 16]
-    float* corr_s = (float*)(p_s + LD_HEADS * (LD_BN * 2 + 16));    // [16]
     constexpr int PP = LD_BN * 2 + 16;
+    unsigned char* q_s = sm;                                        // [HEADS][pitch]
+    unsigned char* k_s = q_s + HEADS * pitch;                       // [2][LD_BN][pitch]
+    float* s_s = (float*)(k_s + 2 * LD_BN * pitch);                 // [HEADS][LD_BN]
+    unsigned char* p_s = (unsigned char*)(s_s + HEADS * LD_BN);     // [HEADS][PP]
+    float* corr_s = (float*)(p_s + HEADS * PP);                     // [HEADS]
     const int b = blockIdx.x, hg = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h0 = hg * LD_HEADS, nh = min(LD_HEADS, a.heads - h0);
+    const int h0 = hg * HEADS, nh = min(HEADS, a.heads - h0);
     pdl_wait();
     const int len = a.len_after[b];
     int per = (len + a.n_splits - 1) / a.n_splits;
@@ -304,7 +311,7 @@ __global__ void __launch_bounds__(LD_WARPS * 32) latent_decode_mma_kernel(Latent
     auto load = [&](int stage, int j0) {
         const bf16* src = pool + ((size_t)pt[j0 / a.page_rows] * a.page_rows + (j0 % a.page_rows)) * KD;
         unsigned char* dst = k_s + (size_t)stage * LD_BN * pitch;
-        for (int c = threadIdx.x; c < LD_BN * chunks; c += LD_WARPS * 32) {
+        for (int c = threadIdx.x; c < LD_BN * chunks; c += THREADS) {
             const int r = c / chunks, ch = c % chunks;
             ld_cp16(dst + r * pitch + ch * 16, src + (size_t)r * KD + ch * 8, j0 + r < end);
         }
@@ -313,19 +320,22 @@ __global__ void __launch_bounds__(LD_WARPS * 32) latent_decode_mma_kernel(Latent
     if (beg < end) load(0, beg);
     {   // the queries of this CTA's heads (rows past the last head: zeros)
         const bf16* q = (const bf16*)a.q + (size_t)b * a.q_stride + (size_t)h0 * KD;
-        for (int c = threadIdx.x; c < LD_HEADS * chunks; c += LD_WARPS * 32) {
+        for (int c = threadIdx.x; c < HEADS * chunks; c += THREADS) {
             const int r = c / chunks, ch = c % chunks;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (r < nh) v = *(const uint4*)(q + (size_t)r * KD + ch * 8);
             *(uint4*)(q_s + r * pitch + ch * 16) = v;
         }
     }
-    float o[NP * 2][4];
+    float o[MT][NP * 2][4];
 #pragma unroll
-    for (int n = 0; n < NP * 2; n++) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    for (int m = 0; m < MT; m++)
+#pragma unroll
+        for (int n = 0; n < NP * 2; n++) { o[m][n][0] = o[m][n][1] = o[m][n][2] = o[m][n][3] = 0.f; }
     float m_run[4], l_run[4];                                       // of heads 4 * warp + i (every lane holds a copy)
 #pragma unroll
     for (int i = 0; i < 4; i++) { m_run[i] = -INFINITY; l_run[i] = 0.f; }
+    const int sm_tile = warp / 4, sn_tile = warp % 4;               // scores: this warp's 16 heads and 8 keys
     const int n_tiles = beg < end ? (end - beg + LD_BN - 1) / LD_BN : 0;
     for (int it = 0; it < n_tiles; it++) {
         const int j0 = beg + it * LD_BN;
@@ -333,18 +343,30 @@ __global__ void __launch_bounds__(LD_WARPS * 32) latent_decode_mma_kernel(Latent
         else asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
         const unsigned char* kt = k_s + (size_t)(it & 1) * LD_BN * pitch;
-        // ---- scores of this warp's 8 keys for all 16 heads
-        float sc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int ks = 0; ks < KD / 16; ks++) {
-            uint32_t fa[4], b0, b1;
-            ld_ldsm4(ld_smem(q_s + (lane & 15) * pitch + (ks * 16 + (lane >> 4) * 8) * 2), fa[0], fa[1], fa[2], fa[3]);
-            ld_ldsm2(ld_smem(kt + (warp * 8 + (lane & 7)) * pitch + (ks * 16 + ((lane >> 3) & 1) * 8) * 2), b0, b1);
-            ld_mma(sc, fa, b0, b1);
+        // ---- scores
+        float sc[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) { sc[u][0] = sc[u][1] = sc[u][2] = sc[u][3] = 0.f; }
+        const uint32_t qa = ld_smem(q_s + (sm_tile * 16 + (lane & 15)) * pitch + (lane >> 4) * 16);
+        const uint32_t ka = ld_smem(kt + (sn_tile * 8 + (lane & 7)) * pitch + ((lane >> 3) & 1) * 16);
+        const int ksteps = KD / 16;
+        for (int ks = 0; ks < ksteps; ks += 4) {
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if (ks + u < ksteps) {
+                    uint32_t fa[4], b0, b1;
+                    ld_ldsm4(qa + (ks + u) * 32, fa[0], fa[1], fa[2], fa[3]);
+                    ld_ldsm2(ka + (ks + u) * 32, b0, b1);
+                    ld_mma(sc[u], fa, b0, b1);
+                }
+            }
         }
         {
-            const int r = lane >> 2, cc = warp * 8 + (lane & 3) * 2;
-            s_s[r * LD_BN + cc] = sc[0] * a.scale; s_s[r * LD_BN + cc + 1] = sc[1] * a.scale;
-            s_s[(r + 8) * LD_BN + cc] = sc[2] * a.scale; s_s[(r + 8) * LD_BN + cc + 1] = sc[3] * a.scale;
+            const int r = sm_tile * 16 + (lane >> 2), cc = sn_tile * 8 + (lane & 3) * 2;
+            s_s[r * LD_BN + cc] = (sc[0][0] + sc[1][0] + sc[2][0] + sc[3][0]) * a.scale;
+            s_s[r * LD_BN + cc + 1] = (sc[0][1] + sc[1][1] + sc[2][1] + sc[3][1]) * a.scale;
+            s_s[(r + 8) * LD_BN + cc] = (sc[0][2] + sc[1][2] + sc[2][2] + sc[3][2]) * a.scale;
+            s_s[(r + 8) * LD_BN + cc + 1] = (sc[0][3] + sc[1][3] + sc[2][3] + sc[3][3]) * a.scale;
         }
         __syncthreads();
         // ---- softmax of four heads per warp over the tile's 32 keys (one key per lane)
@@ -361,40 +383,46 @@ __global__ void __launch_bounds__(LD_WARPS * 32) latent_decode_mma_kernel(Latent
             if (lane == 0) corr_s[r] = corr;
         }
         __syncthreads();
-        // ---- O = O * corr + P C, this warp's share of the latent's columns
-        const float ca = corr_s[lane >> 2], cb = corr_s[(lane >> 2) + 8];
-        uint32_t pa[LD_BN / 16][4];
+        // ---- O = O * corr + P C, this warp's share of the latent's columns, for every tile of heads
 #pragma unroll
-        for (int kk = 0; kk < LD_BN / 16; kk++)
-            ld_ldsm4(ld_smem(p_s + (lane & 15) * PP + (kk * 16 + (lane >> 4) * 8) * 2), pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3]);
+        for (int m = 0; m < MT; m++) {
+            const float ca = corr_s[m * 16 + (lane >> 2)], cb = corr_s[m * 16 + (lane >> 2) + 8];
+            uint32_t pa[LD_BN / 16][4];
 #pragma unroll
-        for (int j = 0; j < NP; j++) {
-            const int col0 = (j * LD_WARPS + warp) * 16;
-            if (col0 >= C) continue;
-            float* oa = o[2 * j]; float* ob = o[2 * j + 1];
-            oa[0] *= ca; oa[1] *= ca; oa[2] *= cb; oa[3] *= cb; ob[0] *= ca; ob[1] *= ca; ob[2] *= cb; ob[3] *= cb;
+            for (int kk = 0; kk < LD_BN / 16; kk++)
+                ld_ldsm4(ld_smem(p_s + (m * 16 + (lane & 15)) * PP + (kk * 16 + (lane >> 4) * 8) * 2), pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3]);
 #pragma unroll
-            for (int kk = 0; kk < LD_BN / 16; kk++) {
-                uint32_t b0, b1, b2, b3;
-                ld_ldsm4_t(ld_smem(kt + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * pitch + (col0 + (lane >> 4) * 8) * 2), b0, b1, b2, b3);
-                ld_mma(oa, pa[kk], b0, b1);
-                ld_mma(ob, pa[kk], b2, b3);
+            for (int j = 0; j < NP; j++) {
+                const int col0 = (j * WARPS + warp) * 16;
+                if (col0 >= C) continue;
+                float* oa = o[m][2 * j]; float* ob = o[m][2 * j + 1];
+                oa[0] *= ca; oa[1] *= ca; oa[2] *= cb; oa[3] *= cb; ob[0] *= ca; ob[1] *= ca; ob[2] *= cb; ob[3] *= cb;
+#pragma unroll
+                for (int kk = 0; kk < LD_BN / 16; kk++) {
+                    uint32_t b0, b1, b2, b3;
+                    ld_ldsm4_t(ld_smem(kt + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * pitch + (col0 + (lane >> 4) * 8) * 2), b0, b1, b2, b3);
+                    ld_mma(oa, pa[kk], b0, b1);
+                    ld_mma(ob, pa[kk], b2, b3);
+                }
             }
         }
         __syncthreads();                                            // the load after next overwrites this stage; s_s and p_s are free
     }
     // ---- partial results: [b][h][split][C + 2]
-    const int ra = lane >> 2, rb = ra + 8;
 #pragma unroll
-    for (int j = 0; j < NP; j++) {
-        const int col0 = (j * LD_WARPS + warp) * 16;
-        if (col0 >= C) continue;
+    for (int m = 0; m < MT; m++) {
+        const int ra = m * 16 + (lane >> 2), rb = ra + 8;
 #pragma unroll
-        for (int half = 0; half < 2; half++) {
-            const int col = col0 + half * 8 + (lane & 3) * 2;
-            const float* acc = o[2 * j + half];
-            if (ra < nh) { float* p = a.partial + (((size_t)b * a.heads + h0 + ra) * a.n_splits + split) * (C + 2); p[col] = acc[0]; p[col + 1] = acc[1]; }
-            if (rb < nh) { float* p = a.partial + (((size_t)b * a.heads + h0 + rb) * a.n_splits + split) * (C + 2); p[col] = acc[2]; p[col + 1] = acc[3]; }
+        for (int j = 0; j < NP; j++) {
+            const int col0 = (j * WARPS + warp) * 16;
+            if (col0 >= C) continue;
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                const int col = col0 + half * 8 + (lane & 3) * 2;
+                const float* acc = o[m][2 * j + half];
+                if (ra < nh) { float* p = a.partial + (((size_t)b * a.heads + h0 + ra) * a.n_splits + split) * (C + 2); p[col] = acc[0]; p[col + 1] = acc[1]; }
+                if (rb < nh) { float* p = a.partial + (((size_t)b * a.heads + h0 + rb) * a.n_splits + split) * (C + 2); p[col] = acc[2]; p[col + 1] = acc[3]; }
+            }
         }
     }
     if (lane == 0) {
@@ -418,15 +446,17 @@ extern "C" int tb_latent_decode_mma(const LatentDecodeArgs* args, int batch, cud
         return tb_refuse("latent_decode_mma: n_splits=%d needs scratch; pages of %d rows", a.n_splits, a.page_rows);
     if (((uintptr_t)a.q & 15) || (a.q_stride % 8) || ((uintptr_t)a.pool & 15)) return tb_refuse("latent_decode_mma: rows must be 16-byte aligned");
     const int KD = a.C + a.R, pitch = KD * 2 + 16;
-    const size_t smem = (size_t)LD_HEADS * pitch + 2 * (size_t)LD_BN * pitch + LD_HEADS * LD_BN * 4 + LD_HEADS * (LD_BN * 2 + 16) + LD_HEADS * 4;
-    const int np = (a.C + 63) / 64;
-    dim3 grid(batch, (a.heads + LD_HEADS - 1) / LD_HEADS, a.n_splits);
-#define LD_MMA(N) do { \
+    const int mt = a.heads > 16 ? 2 : 1, heads_cta = 16 * mt, warps = 4 * mt;
+    const size_t smem = (size_t)heads_cta * pitch + 2 * (size_t)LD_BN * pitch + heads_cta * LD_BN * 4 + heads_cta * (LD_BN * 2 + 16) + heads_cta * 4;
+    const int np = (a.C + 16 * warps - 1) / (16 * warps);
+    dim3 grid(batch, (a.heads + heads_cta - 1) / heads_cta, a.n_splits);
+#define LD_MMA(N, M) do { \
         static bool set = false; \
-        if (!set) { cudaError_t e = cudaFuncSetAttribute(latent_decode_mma_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+        if (!set) { cudaError_t e = cudaFuncSetAttribute(latent_decode_mma_kernel<N, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
                     if (e != cudaSuccess) return (int)e; set = true; } \
-        tb_launch(latent_decode_mma_kernel<N>, dim3(grid), dim3(LD_WARPS * 32), smem, stream, a); } while (0)
-    if (np <= 2) LD_MMA(2); else if (np <= 4) LD_MMA(4); else LD_MMA(8);
+        tb_launch(latent_decode_mma_kernel<N, M>, dim3(grid), dim3(warps * 32), smem, stream, a); } while (0)
+    if (mt == 1) { if (np <= 2) LD_MMA(2, 1); else if (np <= 4) LD_MMA(4, 1); else LD_MMA(8, 1); }
+    else { if (np <= 1) LD_MMA(1, 2); else if (np <= 2) LD_MMA(2, 2); else LD_MMA(4, 2); }
     int st = tb_launch_status();
     if (st) return st;
     tb_launch(latent_combine_kernel<bf16>, dim3(batch, a.heads), dim3(128), 0, stream, a);

@@ -54,6 +54,10 @@ struct GemmParams {
     float scale;                     // the output times this (1 for a plain product); after the cap, never with it
     int act;                         // gated epilogue: 0 gelu_tanh, 1 silu, 2 clamped_swish (only with GATED kernels)
     float limit;                     // clamped_swish: both branches are bounded by it
+    // Grouped products (token-major tiles only): tile tp of the tokens multiplies the weight rows of group
+    // tile_group[tp], which start at row tile_group[tp] * group_rows of the weight operand.  Null: one group.
+    const int* tile_group;
+    int group_rows;
 };
 
 // Gated epilogue.  The weight rows are interleaved in blocks of 16: [gate 0..15 | up 0..15 | gate 16..31 | ...],
@@ -221,7 +225,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 int tp, tq, sp; decode(item, tp, tq, sp);
                 const int kb0 = sp * p.kb_per_split, kb1 = min(p.kblocks, kb0 + p.kb_per_split);
-                const int w_row = SWAP ? tp * BM : tq * BN, a_row = SWAP ? tq * BN : tp * BM;
+                int w_row = SWAP ? tp * BM : tq * BN;
+                const int a_row = SWAP ? tq * BN : tp * BM;
+                if (!SWAP && p.tile_group != nullptr) {
+                    // the table of groups is the preceding kernel's work: nothing is fetched before it is there
+                    if (!waited) { pdl_wait(); waited = true; }
+                    w_row += p.tile_group[tp] * p.group_rows;
+                }
                 int kb = kb0;
                 if (!waited) {
                     // Weights do not depend on the kernel before this one: start streaming them into the
@@ -715,6 +725,7 @@ extern "C" int tb_gemm_tc_ex(const void* A, const void* W, void* C, int c_dtype,
     else bn = N >= 256 ? 256 : 128;
 
     GemmParams p;
+    p.tile_group = nullptr; p.group_rows = 0;
     p.K = K; p.kblocks = kblocks; p.splits = splits; p.kb_per_split = per;
     p.out = C; p.ld_out = ldc; p.partial = scratch; p.cap = splits > 1 ? 0.f : softcap;
     p.act = gated ? gated_act : 0;
@@ -771,6 +782,44 @@ extern "C" int tb_gemm_tc_ex(const void* A, const void* W, void* C, int c_dtype,
         st = tb_launch_status();
     }
     return st;
+}
+
+// Grouped products: C[m, :] = A[m, :] W_g^T for the group g = tile_group[m / 128] of the 128-row tile that holds row m.
+// W holds `groups` matrices of N rows each, one after the other ([groups * N, K]); rows of A are ordered so that every
+// tile of 128 belongs to one group.  gated_act >= 0: the gated epilogue on rows interleaved per group (N = 2 x the
+// output's width, bfloat16 out); else a plain product into C (bfloat16 or float32).  tile_group: device memory,
+// [ceil(M / 128)] group numbers in [0, groups).
+extern "C" int tb_gemm_tc_grouped(const void* A, const void* W, void* C, int c_dtype, int M, int N, int groups, int K,
+                                  long long lda, long long ldw, long long ldc, const int* tile_group, int gated_act,
+                                  cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || groups <= 0) return 0;
+    if (!tb_gemm_tc_takes(A, W, M, N, K, lda, ldw))
+        return tb_refuse("gemm_tc_grouped: needs K, lda, ldw multiples of 8 and 16-byte aligned operands");
+    if (c_dtype != TB_F32 && c_dtype != TB_BF16) return tb_refuse("gemm_tc_grouped: unknown output dtype %d", c_dtype);
+    if (tile_group == nullptr) return tb_refuse("gemm_tc_grouped: no table of groups");
+    if ((long long)groups * N > 2147483647LL) return tb_refuse("gemm_tc_grouped: %d groups of %d rows", groups, N);
+    const bool gated = gated_act >= 0;
+    if (gated && (gated_act > 1 || N % 32 || c_dtype != TB_BF16))
+        return tb_refuse("gemm_tc_grouped: the gated epilogue (gelu_tanh or silu) needs a multiple of 32 weight rows and writes bfloat16");
+    if (!g_sms) {
+        int dev = 0; cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (g_sms <= 0) g_sms = 148;
+    }
+    const int bn = N >= 256 ? 256 : 128;
+    GemmParams p;
+    p.tile_group = tile_group; p.group_rows = N;
+    p.K = K; p.kblocks = (K + BK - 1) / BK; p.splits = 1; p.kb_per_split = p.kblocks;
+    p.out = C; p.ld_out = ldc; p.partial = nullptr; p.cap = 0.f; p.scale = 1.0f;
+    p.act = gated ? gated_act : 0; p.limit = 0.f;
+    p.rows_p = M; p.rows_q = N;
+    CUtensorMap mp, mq;
+    if (make_map(&mp, A, M, K, lda, BM) || make_map(&mq, W, groups * N, K, ldw, bn)) return -1;
+    p.tiles_p = (M + BM - 1) / BM;
+    p.tiles_q = (N + bn - 1) / bn;
+    if (gated) return bn == 256 ? launch<256, false, bf16, true>(mp, mq, p, stream) : launch<128, false, bf16, true>(mp, mq, p, stream);
+    if (c_dtype == TB_BF16) return bn == 256 ? launch<256, false, bf16>(mp, mq, p, stream) : launch<128, false, bf16>(mp, mq, p, stream);
+    return bn == 256 ? launch<256, false, float>(mp, mq, p, stream) : launch<128, false, float>(mp, mq, p, stream);
 }
 
 extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,

@@ -25,21 +25,50 @@ __global__ void __launch_bounds__(256) add_layernorm_kernel(float* __restrict__ 
     pdl_wait();
     float* hr = h + row * width;
     float sum = 0.f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float v = hr[c];
-        if (a != nullptr) {
-            for (int s = 0; s < n_splits; s++) v += to_f<TA>(a[(size_t)s * split_stride + row * width + c]);
-            hr[c] = v;
+    const bool vec = (width & 3) == 0 && sizeof(TA) == 4;           // 16-byte pieces: rows of 32-bit numbers, width a multiple of 4
+    if (vec) {
+        for (int c = threadIdx.x * 4; c < width; c += blockDim.x * 4) {
+            float4 v = *(const float4*)(hr + c);
+            if (a != nullptr) {
+                for (int s = 0; s < n_splits; s++) {
+                    const float4 u = *(const float4*)((const float*)a + (size_t)s * split_stride + row * width + c);
+                    v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+                }
+                *(float4*)(hr + c) = v;
+            }
+            *(float4*)(row_s + c) = v;
+            sum += (v.x + v.y) + (v.z + v.w);
         }
-        row_s[c] = v;
-        sum += v;
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            float v = hr[c];
+            if (a != nullptr) {
+                for (int s = 0; s < n_splits; s++) v += to_f<TA>(a[(size_t)s * split_stride + row * width + c]);
+                hr[c] = v;
+            }
+            row_s[c] = v;
+            sum += v;
+        }
     }
     const float mean = block_sum(sum, red) / (float)width;
     float sq = 0.f;
     for (int c = threadIdx.x; c < width; c += blockDim.x) { const float d = row_s[c] - mean; sq = fmaf(d, d, sq); }
     const float rstd = 1.f / sqrtf(block_sum(sq, red) / (float)width + eps);
     TO* yr = y + row * width;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) yr[c] = from_f<TO>((row_s[c] - mean) * rstd * w[c] + b[c]);
+    if ((width & 3) == 0) {
+        for (int c = threadIdx.x * 4; c < width; c += blockDim.x * 4) {
+            const float4 v = *(const float4*)(row_s + c), ww = *(const float4*)(w + c), bb = *(const float4*)(b + c);
+            const float o0 = (v.x - mean) * rstd * ww.x + bb.x, o1 = (v.y - mean) * rstd * ww.y + bb.y;
+            const float o2 = (v.z - mean) * rstd * ww.z + bb.z, o3 = (v.w - mean) * rstd * ww.w + bb.w;
+            if (sizeof(TO) == 4) *(float4*)((float*)yr + c) = make_float4(o0, o1, o2, o3);
+            else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1), hi = __floats2bfloat162_rn(o2, o3);
+                *(uint2*)((bf16*)yr + c) = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) yr[c] = from_f<TO>((row_s[c] - mean) * rstd * w[c] + b[c]);
+    }
 }
 
 __global__ void add_rows_kernel(float* __restrict__ h, const float* __restrict__ rows, const float* __restrict__ vec,

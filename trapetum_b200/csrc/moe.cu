@@ -375,6 +375,102 @@ __global__ void moe_sum_pairs_kernel(const float* __restrict__ pair_out, const f
     out[i] = acc;
 }
 
+// ---------------------------------------------------------------------------
+// The same grouping for the tcgen05 product (gemm_tc.cu, grouped mode): the pairs are laid out expert by expert
+// with every expert's stretch padded to whole tiles of 128 rows, so that a tile of the product's token operand
+// belongs to one expert.  tb_moe_group_padded makes the layout (where every pair goes, which pair every row
+// holds, every tile's expert), tb_moe_gather_rows fills the operand, and tb_moe_combine_sorted adds a token's
+// weighted expert outputs (and the shared expert) back up.
+// ---------------------------------------------------------------------------
+struct MoePadArgs {
+    const int* idx;            // [P] expert of every pair
+    int* pos;                  // [P] the pair's row in the padded order
+    int* row_pair;             // [max_rows] the pair a row holds, -1 for padding
+    int* tile_group;           // [max_rows / 128] the tile's expert (0 for tiles past the last one)
+    int P, E, max_rows;
+};
+
+__global__ void __launch_bounds__(1024) moe_group_padded_kernel(MoePadArgs a) {
+    pdl_launch_dependents();
+    extern __shared__ int sm[];                       // [E] counts, [E] first rows, [E] cursors
+    int* cnt = sm; int* off = sm + a.E; int* cur = sm + 2 * a.E;
+    for (int e = threadIdx.x; e < a.E; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
+    __syncthreads();
+    pdl_wait();
+    for (int r = threadIdx.x; r < a.max_rows; r += blockDim.x) a.row_pair[r] = -1;
+    for (int t = threadIdx.x; t < a.max_rows / 128; t += blockDim.x) a.tile_group[t] = 0;
+    for (int p = threadIdx.x; p < a.P; p += blockDim.x) atomicAdd(&cnt[a.idx[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int o = 0;
+        for (int e = 0; e < a.E; e++) { off[e] = o; o += (cnt[e] + 127) / 128 * 128; }
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < a.P; p += blockDim.x) {
+        const int e = a.idx[p];
+        const int r = off[e] + atomicAdd(&cur[e], 1);
+        a.pos[p] = r; a.row_pair[r] = p;
+    }
+    for (int e = threadIdx.x; e < a.E; e += blockDim.x)
+        for (int t = off[e] / 128; t < (off[e] + cnt[e] + 127) / 128; t++) a.tile_group[t] = e;
+}
+
+__global__ void __launch_bounds__(128) moe_gather_rows_kernel(const bf16* __restrict__ x, long long x_stride, const int* __restrict__ row_pair,
+                                                              bf16* __restrict__ out, int W, int top) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int p = row_pair[r];
+    uint4* dst = (uint4*)(out + (size_t)r * W);
+    if (p < 0) { for (int c = threadIdx.x; c < W / 8; c += blockDim.x) dst[c] = make_uint4(0, 0, 0, 0); return; }
+    const uint4* src = (const uint4*)(x + (size_t)(p / top) * x_stride);
+    for (int c = threadIdx.x; c < W / 8; c += blockDim.x) dst[c] = src[c];
+}
+
+__global__ void moe_combine_sorted_kernel(const float* __restrict__ y, const int* __restrict__ pos, const float* __restrict__ weight,
+                                          const float* __restrict__ shared, int shared_splits, long long shared_split_stride,
+                                          const float* __restrict__ gate, float* __restrict__ out, long long n, int W, int top) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long t = i / W; const int c = (int)(i % W);
+    float acc = 0.f;
+    for (int k = 0; k < top; k++) acc = fmaf(weight[t * top + k], y[(size_t)pos[t * top + k] * W + c], acc);   // in the order of the choice
+    if (shared != nullptr) {
+        float sh = 0.f;
+        for (int s = 0; s < shared_splits; s++) sh += shared[(size_t)s * shared_split_stride + i];
+        acc = fmaf(gate[t], sh, acc);
+    }
+    out[i] = acc;
+}
+
+extern "C" int tb_moe_group_padded(const MoePadArgs* args, cudaStream_t stream) {
+    const MoePadArgs& a = *args;
+    if (a.P <= 0) return 0;
+    if (a.E <= 0 || a.E > 2048 || a.max_rows % 128 || a.max_rows < a.P) return tb_refuse("moe_group_padded: experts=%d rows=%d", a.E, a.max_rows);
+    tb_launch(moe_group_padded_kernel, dim3(1), dim3(1024), (size_t)3 * a.E * sizeof(int), stream, a);
+    return tb_launch_status();
+}
+
+extern "C" int tb_moe_gather_rows(const void* x, long long x_stride, const int* row_pair, void* out, int rows, int W, int top,
+                                  cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (W % 8 || x_stride % 8 || ((uintptr_t)x & 15) || ((uintptr_t)out & 15)) return tb_refuse("moe_gather_rows: rows must be 16-byte aligned");
+    tb_launch(moe_gather_rows_kernel, dim3(rows), dim3(128), 0, stream, (const bf16*)x, x_stride, row_pair, (bf16*)out, W, top);
+    return tb_launch_status();
+}
+
+extern "C" int tb_moe_combine_sorted(const float* y, const int* pos, const float* weight, const float* shared, int shared_splits,
+                                     long long shared_split_stride, const float* gate, float* out, int n_tokens, int W, int top,
+                                     cudaStream_t stream) {
+    const long long n = (long long)n_tokens * W;
+    if (n <= 0) return 0;
+    tb_launch(moe_combine_sorted_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, y, pos, weight, shared, shared_splits,
+              shared_split_stride, gate, out, n, W, top);
+    return tb_launch_status();
+}
+
 extern "C" int tb_moe_group(const MoeGroupArgs* args, cudaStream_t stream) {
     const MoeGroupArgs& a = *args;
     if (a.P <= 0) return 0;

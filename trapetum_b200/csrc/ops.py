@@ -1295,7 +1295,7 @@ def latent_decode(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor,
     mma = q.dtype == torch.bfloat16 and bool(lib.tb_latent_decode_mma_takes(c_int(C), c_int(R))) and q.stride(0) % 8 == 0 \
         and q.data_ptr() % 16 == 0
     # pieces: enough CTAs for about two per SM, none shorter than 128 keys (256 on the generic kernel)
-    units = B * ((heads + 15) // 16) if mma else B * heads
+    units = B * ((heads + 31) // 32 if heads > 16 else 1) if mma else B * heads          # the tensor-core kernel: up to 32 heads a CTA
     shortest = 128 if mma else 256
     pieces = max(1, min((len_bucket + shortest - 1) // shortest, max(1, (2 * sm_count(q.device)) // max(1, units))))
     out = torch.empty((B, heads * C), dtype=q.dtype, device=q.device)
@@ -1394,6 +1394,47 @@ def moe_route(logits: torch.Tensor, experts: int, correction: Optional[torch.Ten
 
 
 MOE_GROUPED_FROM = 128      # (token, expert) pairs from which the experts' products run grouped on the tensor cores
+MOE_TCGEN05_FROM = 1024     # ... and from which the grouped products are the tcgen05 kernel's (tiles of 128 rows per expert)
+
+
+class _MoePadArgs(ctypes.Structure):
+    _fields_ = [("idx", c_void_p), ("pos", c_void_p), ("row_pair", c_void_p), ("tile_group", c_void_p),
+                ("P", c_int), ("E", c_int), ("max_rows", c_int)]
+
+
+def _moe_grouped_tc(x, gate_up_w, down_w, idx, weight, shared, gate, out):
+    """The experts' products on the tcgen05 kernel: the pairs ordered by expert, each expert's stretch padded to whole
+    tiles of 128 rows (see moe.cu and gemm_tc.cu's grouped mode).  Shapes depend on the sizes only."""
+    T, W = x.shape
+    E, ff2 = gate_up_w.shape[0], gate_up_w.shape[1]
+    ff = ff2 // 2
+    top = idx.shape[1]
+    P = T * top
+    max_rows = ((P + 127) // 128 + min(E, P)) * 128
+    ints = torch.empty(P + max_rows + max_rows // 128, dtype=torch.int32, device=x.device)
+    pos, row_pair, tile_group = ints[:P], ints[P:P + max_rows], ints[P + max_rows:]
+    lib = build.load("moe")
+    g = _MoePadArgs()
+    g.idx = idx.data_ptr(); g.pos = pos.data_ptr(); g.row_pair = row_pair.data_ptr(); g.tile_group = tile_group.data_ptr()
+    g.P = P; g.E = E; g.max_rows = max_rows
+    _check(lib, lib.tb_moe_group_padded(ctypes.byref(g), _stream()), "moe_group_padded")
+    xs = torch.empty((max_rows, W), dtype=x.dtype, device=x.device)
+    _check(lib, lib.tb_moe_gather_rows(_ptr(x), c_longlong(x.stride(0)), _ptr(row_pair), _ptr(xs), c_int(max_rows), c_int(W),
+                                       c_int(top), _stream()), "moe_gather_rows")
+    act = torch.empty((max_rows, ff), dtype=x.dtype, device=x.device)
+    y = torch.empty((max_rows, W), dtype=torch.float32, device=x.device)
+    gl = build.load("gemm_tc")
+    _check(gl, gl.tb_gemm_tc_grouped(_ptr(xs), _ptr(gate_up_w), _ptr(act), c_int(code(x.dtype)), c_int(max_rows), c_int(ff2),
+                                     c_int(E), c_int(W), c_longlong(W), c_longlong(W), c_longlong(ff), _ptr(tile_group),
+                                     c_int(ACTIVATIONS["silu"]), _stream()), "gemm_tc_grouped")
+    _check(gl, gl.tb_gemm_tc_grouped(_ptr(act), _ptr(down_w), _ptr(y), c_int(code(torch.float32)), c_int(max_rows), c_int(W),
+                                     c_int(E), c_int(ff), c_longlong(ff), c_longlong(ff), c_longlong(W), _ptr(tile_group),
+                                     c_int(-1), _stream()), "gemm_tc_grouped")
+    _check(lib, lib.tb_moe_combine_sorted(_ptr(y), _ptr(pos), _ptr(weight), _ptr(shared),
+                                          c_int(shared.shape[0] if shared is not None else 0),
+                                          c_longlong(shared.stride(0) if shared is not None else 0), _ptr(gate), _ptr(out),
+                                          c_int(T), c_int(W), c_int(top), _stream()), "moe_combine_sorted")
+    return out
 
 
 class _MoeGroupArgs(ctypes.Structure):
@@ -1446,11 +1487,13 @@ class _MoeExpertArgs(ctypes.Structure):
 
 
 def moe_experts(x: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor, down_w: torch.Tensor, idx: torch.Tensor,
-                weight: torch.Tensor, shared: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                weight: torch.Tensor, shared: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                gate_up_w: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The weighted sum of every token's chosen experts ``down_e(silu(gate_e x) * up_e x)`` plus ``gate[t] * shared[t]``
     (``shared`` float32 partial sums [splits, T, W]); returns float32 [T, W].  Expert matrices: ``gate_w``, ``up_w``
-    [E, ff, W] and ``down_w`` [E, W, ff] of x's dtype."""
-    _cuda(x, gate_w, up_w, down_w, idx, weight, shared, gate)
+    [E, ff, W] and ``down_w`` [E, W, ff] of x's dtype; ``gate_up_w`` [E, 2 ff, W]: every expert's gate and up rows
+    interleaved (``interleave_gate_up``), which lets many tokens run on the tcgen05 product."""
+    _cuda(x, gate_w, up_w, down_w, idx, weight, shared, gate, gate_up_w)
     _rows_contig(x, "moe: x")
     T, W = x.shape
     E, ff = gate_w.shape[0], gate_w.shape[1]
@@ -1467,6 +1510,8 @@ def moe_experts(x: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor, down_
     out = torch.empty((T, W), dtype=torch.float32, device=x.device)
     if x.dtype == torch.bfloat16 and T * top >= MOE_GROUPED_FROM and W % 8 == 0 and ff % 8 == 0 and x.stride(0) % 8 == 0 \
             and x.data_ptr() % 16 == 0:
+        if gate_up_w is not None and T * top >= MOE_TCGEN05_FROM and ff % 16 == 0:
+            return _moe_grouped_tc(x, gate_up_w, down_w, idx, weight, shared, gate, out)
         return _moe_grouped(x, gate_w, up_w, down_w, idx, weight, shared, gate, out)
     act = torch.empty((T * top, ff), dtype=x.dtype, device=x.device)
     a = _MoeExpertArgs()

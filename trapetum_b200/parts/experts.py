@@ -79,6 +79,11 @@ class RoutedExperts(FeedForward):
         self.w_gate = torch.stack([tensors[self._expert(e, "gate")].to(dt) for e in range(self.E)]).contiguous()
         self.w_up = torch.stack([tensors[self._expert(e, "up")].to(dt) for e in range(self.E)]).contiguous()
         self.w_down = torch.stack([tensors[self._expert(e, "down")].to(dt) for e in range(self.E)]).contiguous()
+        # for many tokens: every expert's gate and up rows interleaved, as the tensor-core product's gated epilogue
+        # wants them (a second copy of those rows; steps of few tokens read the plain ones)
+        self.w_gate_up = None
+        if dt == torch.bfloat16 and self.rt.dtype == torch.bfloat16 and self.ff % 16 == 0 and self.hidden % 8 == 0:
+            self.w_gate_up = torch.stack([ops.interleave_gate_up(self.w_gate[e], self.w_up[e]) for e in range(self.E)]).contiguous()
         rows = [router]
         self.has_gate = False
         if self.shared is not None:
@@ -105,7 +110,7 @@ class RoutedExperts(FeedForward):
                 gate = ctx.memo.get("ones")
                 if gate is None or gate.numel() < x.shape[0]:
                     gate = ctx.memo["ones"] = torch.ones(x.shape[0], dtype=torch.float32, device=x.device)
-        return ops.moe_experts(x, self.w_gate, self.w_up, self.w_down, idx, weight, shared, gate)
+        return ops.moe_experts(x, self.w_gate, self.w_up, self.w_down, idx, weight, shared, gate, self.w_gate_up)
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)
