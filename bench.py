@@ -504,7 +504,8 @@ def lofirax_kernels(torch, size, hbm_gbs, tokens=PREFILL_TOKENS):
         logits.numel() * 4 + T * top * 8, like="add_rmsnorm")
     idx, wt, gate = ops.moe_route(logits, E, corr, True, top, groups, keep, 2, 1e-20)
     gw, uw, dw = (torch.randn(E, a_, b_, device=dev).to(bf) * .02 for a_, b_ in ((eff, W), (eff, W), (W, eff)))
-    rec("experts (grouped products)", _median_us(torch, lambda: ops.moe_experts(x, gw, uw, dw, idx, wt), flush),
+    gu = torch.stack([ops.interleave_gate_up(gw[e], uw[e]) for e in range(E)]).contiguous()      # as the part binds them
+    rec("experts (grouped products)", _median_us(torch, lambda: ops.moe_experts(x, gw, uw, dw, idx, wt, gate_up_w=gu), flush),
         3 * E * eff * W * 2 + T * W * 2, tensor_flops=2.0 * T * top * 3 * eff * W, like="gated feed-forward (two products)")
     wgu = ops.interleave_gate_up(torch.randn(ff, W, device=dev).to(bf) * .02, torch.randn(ff, W, device=dev).to(bf) * .02)
     wdn = torch.randn(W, ff, device=dev).to(bf) * .02

@@ -29,31 +29,34 @@ struct LatentRowsArgs {
     void* rows;                                                // [T][C + R]
 };
 
-// A warp per token, four tokens per CTA: the row waits in the warp's piece of shared memory between the sum and the write.
 template <typename T>
 __global__ void __launch_bounds__(128) latent_rows_kernel(LatentRowsArgs a) {
     pdl_launch_dependents();
-    extern __shared__ float rows_s[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, W = a.C + a.R;
-    const int t = blockIdx.x * 4 + warp;
-    float* row_s = rows_s + (size_t)warp * W;
+    extern __shared__ float row_s[];
+    __shared__ float red[33];
+    const int t = blockIdx.x, W = a.C + a.R;
     pdl_wait();
-    if (t >= a.n_tokens) return;
     float sq = 0.f;
-    for (int c = lane; c < W; c += 32) {
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float* src = a.dkv + (size_t)t * W + c;
         float v = 0.f;
-        for (int s = 0; s < a.splits; s++) v += a.dkv[(size_t)s * a.split_stride + (size_t)t * W + c];
+        int s = 0;
+        for (; s + 4 <= a.splits; s += 4) {            // four loads on their way at a time, added in split order
+            const float v0 = src[(size_t)s * a.split_stride], v1 = src[(size_t)(s + 1) * a.split_stride];
+            const float v2 = src[(size_t)(s + 2) * a.split_stride], v3 = src[(size_t)(s + 3) * a.split_stride];
+            v = (((v + v0) + v1) + v2) + v3;
+        }
+        for (; s < a.splits; s++) v += src[(size_t)s * a.split_stride];
         row_s[c] = v;
         if (c < a.C) sq = fmaf(v, v, sq);
     }
-    __syncwarp();
-    const float rinv = 1.f / sqrtf(warp_sum(sq) / (float)a.C + a.eps);
+    const float rinv = 1.f / sqrtf(block_sum(sq, red) / (float)a.C + a.eps);     // its barriers also publish row_s
     const int pos = a.positions[t];
     const int page = a.page_table[(size_t)a.token_seq[t] * a.pt_stride + pos / a.page_rows];
     T* cache = (T*)a.pool + ((size_t)page * a.page_rows + pos % a.page_rows) * W;
     T* out = (T*)a.rows + (size_t)t * W;
     const int half = a.rot_dims / 2;
-    for (int c = lane; c < W; c += 32) {
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
         float v;
         if (c < a.C) {
             v = row_s[c] * rinv * a.norm_w[c];
@@ -75,8 +78,10 @@ __global__ void __launch_bounds__(128) latent_rows_kernel(LatentRowsArgs a) {
 }
 
 // ---------------------------------------------------------------------------
-constexpr int HL_TOK = 8;
+constexpr int HL_TOK = 8, HL_ROWS = 4;
 
+// y[t, h, o] = sum_i w[h, o, i] x[t, h, i]: eight tokens per CTA (their x in shared memory), a warp per group of four
+// output rows whose weights are on their way together, 16 bytes per lane and load where the row allows it.
 template <typename T>
 __global__ void __launch_bounds__(128) head_linear_kernel(const T* __restrict__ x, long long x_stride, const T* __restrict__ w,
                                                           T* __restrict__ y, long long y_stride, int n_tokens, int in, int out) {
@@ -92,20 +97,48 @@ __global__ void __launch_bounds__(128) head_linear_kernel(const T* __restrict__ 
     }
     __syncthreads();
     const T* wh = w + (size_t)h * out * in;
-    for (int o = blockIdx.z * nwarp + warp; o < out; o += gridDim.z * nwarp) {
-        float acc[HL_TOK];
+    constexpr int VEC = 16 / sizeof(T);
+    const bool vec = (in % VEC) == 0 && (((uintptr_t)wh) & 15) == 0;
+    for (int o0 = (blockIdx.z * nwarp + warp) * HL_ROWS; o0 < out; o0 += gridDim.z * nwarp * HL_ROWS) {
+        float acc[HL_ROWS][HL_TOK];
 #pragma unroll
-        for (int tt = 0; tt < HL_TOK; tt++) acc[tt] = 0.f;
-        for (int c = lane; c < in; c += 32) {
-            const float wv = to_f<T>(wh[(size_t)o * in + c]);
+        for (int r = 0; r < HL_ROWS; r++)
 #pragma unroll
-            for (int tt = 0; tt < HL_TOK; tt++) acc[tt] = fmaf(wv, x_s[tt * in + c], acc[tt]);
+            for (int tt = 0; tt < HL_TOK; tt++) acc[r][tt] = 0.f;
+        if (vec) {
+            for (int c = lane * VEC; c < in; c += 32 * VEC) {
+                uint4 wv[HL_ROWS];
+#pragma unroll
+                for (int r = 0; r < HL_ROWS; r++)
+                    wv[r] = (o0 + r < out) ? *(const uint4*)(wh + (size_t)(o0 + r) * in + c) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int r = 0; r < HL_ROWS; r++) {
+                    const T* e = (const T*)&wv[r];
+#pragma unroll
+                    for (int k = 0; k < VEC; k++) {
+                        const float wf = to_f<T>(e[k]);
+#pragma unroll
+                        for (int tt = 0; tt < HL_TOK; tt++) acc[r][tt] = fmaf(wf, x_s[tt * in + c + k], acc[r][tt]);
+                    }
+                }
+            }
+        } else {
+            for (int c = lane; c < in; c += 32) {
+#pragma unroll
+                for (int r = 0; r < HL_ROWS; r++) {
+                    const float wf = (o0 + r < out) ? to_f<T>(wh[(size_t)(o0 + r) * in + c]) : 0.f;
+#pragma unroll
+                    for (int tt = 0; tt < HL_TOK; tt++) acc[r][tt] = fmaf(wf, x_s[tt * in + c], acc[r][tt]);
+                }
+            }
         }
 #pragma unroll
-        for (int tt = 0; tt < HL_TOK; tt++) {
-            const float s = warp_sum(acc[tt]);
-            if (lane == 0 && tt < nt) y[(size_t)(t0 + tt) * y_stride + (size_t)h * out + o] = from_f<T>(s);
-        }
+        for (int r = 0; r < HL_ROWS; r++)
+#pragma unroll
+            for (int tt = 0; tt < HL_TOK; tt++) {
+                const float sum = warp_sum(acc[r][tt]);
+                if (lane == 0 && tt < nt && o0 + r < out) y[(size_t)(t0 + tt) * y_stride + (size_t)h * out + o0 + r] = from_f<T>(sum);
+            }
     }
 }
 
@@ -114,7 +147,8 @@ extern "C" int tb_head_linear(const void* x, long long x_stride, const void* w, 
     if (n_tokens <= 0) return 0;
     if (heads <= 0 || heads > 65535 || in <= 0 || out <= 0 || in > 1536)
         return tb_refuse("head_linear: heads=%d in=%d out=%d (in at most 1536)", heads, in, out);
-    const int zs = (out + 63) / 64 < 64 ? (out + 63) / 64 : 64;
+    int zs = (out + 4 * HL_ROWS - 1) / (4 * HL_ROWS);          // a CTA's four warps take 16 rows a round
+    if (zs > 64) zs = 64;
     dim3 grid((n_tokens + HL_TOK - 1) / HL_TOK, heads, zs);
     TB_DISPATCH_1(dtype, T, tb_launch(head_linear_kernel<T>, dim3(grid), dim3(128), (size_t)HL_TOK * in * sizeof(float), stream,
                                       (const T*)x, x_stride, (const T*)w, (T*)y, y_stride, n_tokens, in, out));
@@ -126,7 +160,7 @@ extern "C" int tb_latent_rows(const LatentRowsArgs* args, int dtype, cudaStream_
     if (a.n_tokens <= 0) return 0;
     if (a.C <= 0 || a.R < 0 || a.rot_dims < 0 || a.rot_dims % 2 || a.rot_dims > a.R || a.page_rows <= 0)
         return tb_refuse("latent_rows: C=%d R=%d rot_dims=%d page_rows=%d", a.C, a.R, a.rot_dims, a.page_rows);
-    TB_DISPATCH_1(dtype, T, tb_launch(latent_rows_kernel<T>, dim3((a.n_tokens + 3) / 4), dim3(128), (size_t)4 * (a.C + a.R) * sizeof(float), stream, a));
+    TB_DISPATCH_1(dtype, T, tb_launch(latent_rows_kernel<T>, dim3(a.n_tokens), dim3(128), (size_t)(a.C + a.R) * sizeof(float), stream, a));
     return tb_launch_status();
 }
 
@@ -229,26 +263,48 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(LatentDecodeArgs a) 
 }
 
 template <typename T>
-__global__ void latent_combine_kernel(LatentDecodeArgs a) {
+__global__ void __launch_bounds__(128) latent_combine_kernel(LatentDecodeArgs a) {
     pdl_launch_dependents();
+    __shared__ float f_s[128];                           // e^(m_s - M) of up to 128 splits at a time
+    __shared__ float M_s, L_s;
     pdl_wait();
     const int b = blockIdx.x, h = blockIdx.y, C = a.C, n = a.n_splits;
     const float* p = a.partial + ((size_t)b * a.heads + h) * n * (C + 2);
     const float sink = (a.sink != nullptr) ? a.sink[h] : -INFINITY;
-    float M = sink;
-    for (int s = 0; s < n; s++) M = fmaxf(M, p[(size_t)s * (C + 2) + C]);
-    float L = (sink != -INFINITY) ? expf(sink - M) : 0.f;
-    for (int s = 0; s < n; s++) {
-        const float ms = p[(size_t)s * (C + 2) + C];
-        if (ms != -INFINITY) L += p[(size_t)s * (C + 2) + C + 1] * expf(ms - M);
-    }
-    for (int d = threadIdx.x; d < C; d += blockDim.x) {
-        float o = 0.f;
-        for (int s = 0; s < n; s++) {
+    if (threadIdx.x < 32) {
+        float m = sink;
+        for (int s = threadIdx.x; s < n; s += 32) m = fmaxf(m, p[(size_t)s * (C + 2) + C]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int s = threadIdx.x; s < n; s += 32) {
             const float ms = p[(size_t)s * (C + 2) + C];
-            if (ms != -INFINITY) o += p[(size_t)s * (C + 2) + d] * expf(ms - M);
+            if (ms != -INFINITY) l += p[(size_t)s * (C + 2) + C + 1] * expf(ms - m);
         }
-        ((T*)a.out)[(size_t)b * a.out_stride + (size_t)h * a.out_dim + d] = from_f<T>(o / L);
+        l = warp_sum(l);
+        if (threadIdx.x == 0) { M_s = m; L_s = l + ((sink != -INFINITY) ? expf(sink - m) : 0.f); }
+    }
+    __syncthreads();
+    const float M = M_s, inv = 1.f / L_s;
+    float o[4] = {0.f, 0.f, 0.f, 0.f};                   // columns threadIdx.x + 128 k (C <= 512)
+    for (int s0 = 0; s0 < n; s0 += 128) {
+        const int ns = min(128, n - s0);
+        __syncthreads();
+        if (threadIdx.x < ns) {
+            const float ms = p[(size_t)(s0 + threadIdx.x) * (C + 2) + C];
+            f_s[threadIdx.x] = (ms != -INFINITY) ? expf(ms - M) : 0.f;
+        }
+        __syncthreads();
+        for (int s = 0; s < ns; s++) {
+            const float f = f_s[s];
+            const float* ps = p + (size_t)(s0 + s) * (C + 2);
+#pragma unroll
+            for (int k = 0; k < 4; k++) { const int d = threadIdx.x + 128 * k; if (d < C) o[k] = fmaf(ps[d], f, o[k]); }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const int d = threadIdx.x + 128 * k;
+        if (d < C) ((T*)a.out)[(size_t)b * a.out_stride + (size_t)h * a.out_dim + d] = from_f<T>(o[k] * inv);
     }
 }
 

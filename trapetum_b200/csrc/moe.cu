@@ -47,8 +47,15 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteArgs a) {
     pdl_wait();
     if (t >= a.n_tokens) return;
     for (int e = lane; e < a.E + (a.has_gate ? 1 : 0); e += 32) {
+        const float* src = a.logits + (size_t)t * a.row_stride + e;
         float d = 0.f;
-        for (int sp = 0; sp < a.splits; sp++) d += a.logits[(size_t)sp * a.split_stride + (size_t)t * a.row_stride + e];
+        int sp = 0;
+        for (; sp + 4 <= a.splits; sp += 4) {          // four loads on their way at a time, added in split order
+            const float v0 = src[(size_t)sp * a.split_stride], v1 = src[(size_t)(sp + 1) * a.split_stride];
+            const float v2 = src[(size_t)(sp + 2) * a.split_stride], v3 = src[(size_t)(sp + 3) * a.split_stride];
+            d = (((d + v0) + v1) + v2) + v3;
+        }
+        for (; sp < a.splits; sp++) d += src[(size_t)sp * a.split_stride];
         const float s = 1.f / (1.f + expf(-d));
         if (e < a.E) { score[e] = s; choice[e] = s + (a.correction ? a.correction[e] : 0.f); }
         else a.gate[t] = s;
@@ -118,6 +125,37 @@ struct MoeExpertArgs {
     int n_tokens, W, ff, top;
 };
 
+// 16 bytes of a weight row per lane and load where the row allows it; MV_ROWS rows (and for gate/up both matrices) are on
+// their way together, so that a warp keeps enough bytes in flight to stream an expert's matrices at the memory's speed.
+constexpr int MV_ROWS = 4;
+
+template <typename T>
+__device__ __forceinline__ void mv_dot(const T* __restrict__ w0, long long ld, int n_rows, const float* __restrict__ x_s, int K, int lane,
+                                       float* acc /* [MV_ROWS] */) {
+    constexpr int VEC = 16 / sizeof(T);
+#pragma unroll
+    for (int r = 0; r < MV_ROWS; r++) acc[r] = 0.f;
+    if ((K % VEC) == 0 && ((((uintptr_t)w0) | ((uintptr_t)(ld * sizeof(T)))) & 15) == 0) {
+        for (int c = lane * VEC; c < K; c += 32 * VEC) {
+            uint4 wv[MV_ROWS];
+#pragma unroll
+            for (int r = 0; r < MV_ROWS; r++) wv[r] = r < n_rows ? *(const uint4*)(w0 + (size_t)r * ld + c) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int r = 0; r < MV_ROWS; r++) {
+                const T* e = (const T*)&wv[r];
+#pragma unroll
+                for (int k = 0; k < VEC; k++) acc[r] = fmaf(to_f<T>(e[k]), x_s[c + k], acc[r]);
+            }
+        }
+    } else {
+        for (int c = lane; c < K; c += 32)
+#pragma unroll
+            for (int r = 0; r < MV_ROWS; r++) if (r < n_rows) acc[r] = fmaf(to_f<T>(w0[(size_t)r * ld + c]), x_s[c], acc[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < MV_ROWS; r++) acc[r] = warp_sum(acc[r]);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) moe_gate_up_kernel(MoeExpertArgs a) {
     pdl_launch_dependents();
@@ -131,14 +169,17 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(MoeExpertArgs a) {
     __syncthreads();
     const T* gw = (const T*)a.gate_w + (size_t)e * a.ff * a.W;
     const T* uw = (const T*)a.up_w + (size_t)e * a.ff * a.W;
-    for (int f = blockIdx.y * nwarp + warp; f < a.ff; f += gridDim.y * nwarp) {
-        float g = 0.f, u = 0.f;
-        for (int c = lane; c < a.W; c += 32) {
-            g = fmaf(to_f<T>(gw[(size_t)f * a.W + c]), x_s[c], g);
-            u = fmaf(to_f<T>(uw[(size_t)f * a.W + c]), x_s[c], u);
+    for (int f0 = (blockIdx.y * nwarp + warp) * MV_ROWS; f0 < a.ff; f0 += gridDim.y * nwarp * MV_ROWS) {
+        const int nr = min(MV_ROWS, a.ff - f0);
+        float g[MV_ROWS], u[MV_ROWS];
+        mv_dot<T>(gw + (size_t)f0 * a.W, a.W, nr, x_s, a.W, lane, g);
+        mv_dot<T>(uw + (size_t)f0 * a.W, a.W, nr, x_s, a.W, lane, u);
+        if (lane < nr) {
+            float gv = g[0], uv = u[0];
+#pragma unroll
+            for (int r = 1; r < MV_ROWS; r++) if (lane == r) { gv = g[r]; uv = u[r]; }
+            ((T*)a.act)[(size_t)pair * a.ff + f0 + lane] = from_f<T>(gv / (1.f + expf(-gv)) * uv);
         }
-        g = warp_sum(g); u = warp_sum(u);
-        if (lane == 0) ((T*)a.act)[(size_t)pair * a.ff + f] = from_f<T>(g / (1.f + expf(-g)) * u);
     }
 }
 
@@ -152,20 +193,26 @@ __global__ void __launch_bounds__(256) moe_down_kernel(MoeExpertArgs a) {
     for (int i = threadIdx.x; i < a.top * a.ff; i += blockDim.x)
         a_s[i] = to_f<T>(((const T*)a.act)[(size_t)t * a.top * a.ff + i]) * a.weight[(size_t)t * a.top + i / a.ff];
     __syncthreads();
-    for (int c = blockIdx.y * nwarp + warp; c < a.W; c += gridDim.y * nwarp) {
-        float acc = 0.f;
+    for (int c0 = (blockIdx.y * nwarp + warp) * MV_ROWS; c0 < a.W; c0 += gridDim.y * nwarp * MV_ROWS) {
+        const int nr = min(MV_ROWS, a.W - c0);
+        float acc[MV_ROWS] = {0.f, 0.f, 0.f, 0.f};
         for (int k = 0; k < a.top; k++) {
-            const T* dw = (const T*)a.down_w + ((size_t)a.idx[(size_t)t * a.top + k] * a.W + c) * a.ff;
-            for (int f = lane; f < a.ff; f += 32) acc = fmaf(to_f<T>(dw[f]), a_s[k * a.ff + f], acc);
+            float part[MV_ROWS];
+            mv_dot<T>((const T*)a.down_w + ((size_t)a.idx[(size_t)t * a.top + k] * a.W + c0) * a.ff, a.ff, nr, a_s + (size_t)k * a.ff, a.ff, lane, part);
+#pragma unroll
+            for (int r = 0; r < MV_ROWS; r++) acc[r] += part[r];
         }
-        acc = warp_sum(acc);
-        if (lane == 0) {
+        if (lane < nr) {
+            float v = acc[0];
+#pragma unroll
+            for (int r = 1; r < MV_ROWS; r++) if (lane == r) v = acc[r];
+            const int c = c0 + lane;
             if (a.shared != nullptr) {
                 float sh = 0.f;
                 for (int s = 0; s < a.shared_splits; s++) sh += a.shared[(size_t)s * a.shared_split_stride + (size_t)t * a.W + c];
-                acc = fmaf(a.gate[t], sh, acc);
+                v = fmaf(a.gate[t], sh, v);
             }
-            a.out[(size_t)t * a.W + c] = acc;
+            a.out[(size_t)t * a.W + c] = v;
         }
     }
 }
@@ -522,7 +569,8 @@ extern "C" int tb_moe_gate_up(const MoeExpertArgs* args, int dtype, cudaStream_t
     const MoeExpertArgs& a = *args;
     if (a.n_tokens <= 0) return 0;
     if (a.W <= 0 || a.W > 12288 || a.ff <= 0 || a.top <= 0) return tb_refuse("moe: W=%d ff=%d top=%d", a.W, a.ff, a.top);
-    const int ys = (a.ff + 63) / 64 < 32 ? (a.ff + 63) / 64 : 32;
+    const int per = 8 * MV_ROWS;                       // rows a CTA's eight warps take in one round
+    const int ys = (a.ff + per - 1) / per < 64 ? (a.ff + per - 1) / per : 64;
     TB_DISPATCH_1(dtype, T, tb_launch(moe_gate_up_kernel<T>, dim3(a.n_tokens * a.top, ys), dim3(256), (size_t)a.W * sizeof(float), stream, a));
     return tb_launch_status();
 }
@@ -532,7 +580,8 @@ extern "C" int tb_moe_down(const MoeExpertArgs* args, int dtype, cudaStream_t st
     if (a.n_tokens <= 0) return 0;
     const size_t smem = (size_t)a.top * a.ff * sizeof(float);
     if (smem > 48 * 1024) return tb_refuse("moe_down: top=%d x ff=%d activations exceed one block's shared memory", a.top, a.ff);
-    const int ys = (a.W + 63) / 64 < 32 ? (a.W + 63) / 64 : 32;
+    const int per = 8 * MV_ROWS;
+    const int ys = (a.W + per - 1) / per < 64 ? (a.W + per - 1) / per : 64;
     TB_DISPATCH_1(dtype, T, tb_launch(moe_down_kernel<T>, dim3(a.n_tokens, ys), dim3(256), smem, stream, a));
     return tb_launch_status();
 }
