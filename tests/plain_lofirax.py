@@ -108,22 +108,50 @@ def latent_attention(h, m: dict, t: Dict[str, torch.Tensor], p: str, eps: float,
     return o @ t[p + "o"].T, (c, k_rot)
 
 
+MARGINS = None          # a list to collect, per router call, every token's smallest margin (see route)
+
+
 def route(h, r: dict, t: Dict[str, torch.Tensor], p: str):
-    """(chosen experts [tokens, top], their weights [tokens, top])."""
+    """(chosen experts [tokens, top], their weights [tokens, top]).  If MARGINS is a list, also appends [tokens]: how far
+    the choice was from going another way (the last winner's lead over the best loser, and the last kept group's lead
+    over the best group left out), so that a test can set aside tokens whose choice a rounding error may turn."""
     E, top = r["experts"], r["top"]
     s = torch.sigmoid(h @ t[p + "router"].T)
     choice = s + t[p + "correction"]
+    margin = torch.full((h.shape[0],), float("inf"), dtype=F)
     g = r.get("groups")
     if g:
         per = E // g["count"]
         grouped = choice.view(-1, g["count"], per)
         gs = grouped.topk(min(2, per), dim=-1).values.sum(-1)
         keep = gs.topk(g["keep"], dim=-1).indices
+        if g["keep"] < g["count"]:
+            both = gs.topk(g["keep"] + 1, dim=-1).values
+            margin = both[:, -2] - both[:, -1]
         ok = torch.zeros_like(gs, dtype=torch.bool).scatter_(1, keep, True)
         choice = grouped.masked_fill(~ok[..., None], float("-inf")).reshape(-1, E)
     idx = choice.topk(top, dim=-1).indices
+    if top < E:
+        both = choice.topk(top + 1, dim=-1).values
+        margin = torch.minimum(margin, both[:, -2] - both[:, -1])
+    if MARGINS is not None:
+        MARGINS.append(margin)
     w = s.gather(1, idx)
     return idx, w / (w.sum(-1, keepdim=True) + 1e-20)
+
+
+def routing_margins(cfg: dict, tensors, ids) -> torch.Tensor:
+    """Per position: the smallest margin of any of its routing decisions (infinite for a model without experts)."""
+    global MARGINS
+    MARGINS = []
+    try:
+        forward(cfg, tensors, ids)
+        out = torch.full((len(ids),), float("inf"), dtype=F)
+        for m in MARGINS:
+            out = torch.minimum(out, m)
+        return out
+    finally:
+        MARGINS = None
 
 
 def moe(h, mlp: dict, t: Dict[str, torch.Tensor], p: str, rnd=same):

@@ -282,7 +282,7 @@ def test_the_residual_stream_after_every_layer_run(folders, oracles, name, monke
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name, first", [("A", 1), ("A", 2), ("B", 63), ("B", 64), ("C", 65), ("C", 7)])
+@pytest.mark.parametrize("name, first", [("A", 1), ("A", 2), ("B", 63), ("B", 64), ("C", 65), ("C", 7), ("D", 3)])
 def test_prompt_then_token_by_token(folders, oracles, name, first, dtype):
     """Decoding runs across a page's border (64, 128) and through the capture of the step's graph."""
     cfg, w = oracles[name]

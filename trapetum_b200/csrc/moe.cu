@@ -579,7 +579,12 @@ extern "C" int tb_moe_down(const MoeExpertArgs* args, int dtype, cudaStream_t st
     const MoeExpertArgs& a = *args;
     if (a.n_tokens <= 0) return 0;
     const size_t smem = (size_t)a.top * a.ff * sizeof(float);
-    if (smem > 48 * 1024) return tb_refuse("moe_down: top=%d x ff=%d activations exceed one block's shared memory", a.top, a.ff);
+    if (smem > 200 * 1024) return tb_refuse("moe_down: top=%d x ff=%d activations exceed one block's shared memory", a.top, a.ff);
+    if (smem > 48 * 1024) {
+        cudaError_t e = dtype == TB_BF16 ? cudaFuncSetAttribute(moe_down_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+                                         : cudaFuncSetAttribute(moe_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return (int)e;
+    }
     const int per = 8 * MV_ROWS;
     const int ys = (a.W + per - 1) / per < 64 ? (a.W + per - 1) / per : 64;
     TB_DISPATCH_1(dtype, T, tb_launch(moe_down_kernel<T>, dim3(a.n_tokens, ys), dim3(256), smem, stream, a));
