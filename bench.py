@@ -342,10 +342,10 @@ LOFIRAX_RANK = 16
 def lofirax_config(size):
     W, L, _, _, _, ff, _, _, _, V = DESIGN_SIZES[size]
     gh, gd, gv, lh, ld, lr, lv, lc, E, top, eff, groups, keep, sff = LOFIRAX_SIZES[size]
-    gla = {"type": "gla", "mixer": {"heads": gh, "dim": gd, "vdim": gv, "tau": 16.0, "rank": LOFIRAX_RANK},
+    gla = {"type": "gla", "mixer": {"heads": gh, "dim": gd, "vdim": gv, "tau": 8.0, "rank": LOFIRAX_RANK},
            "mlp": {"kind": "dense", "ff": ff}}
     lat = {"type": "latent_attention", "mixer": {"heads": lh, "dim": ld, "rot_dim": lr, "vdim": lv, "kv_rank": lc,
-                                                 "scale": (ld + lr) ** -0.5, "rot": {"base": 500000.0, "dims": lr}},
+                                                 "scale": (ld + lr) ** -0.5, "rot": {"base": 10000.0, "dims": lr}},
            "mlp": {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "top": top, "groups": {"count": groups, "keep": keep}},
                    "shared": {"ff": sff}}}
     # the first two layers run twice: L layer runs from L - 2 layers
@@ -431,7 +431,7 @@ def lofirax_kernels(torch, size, hbm_gbs, tokens=PREFILL_TOKENS):
     a2, a2b, nw = f32(HD, LOFIRAX_RANK) * .3, f32(HD) + 2, torch.ones(gv, device=dev)
     gstate = torch.zeros(1, HD * gv, device=dev)
     rec("gla (decay, scan, gated norm)",
-        _median_us(torch, lambda: ops.gla(proj, low, a2, a2b, 16.0, gd ** -0.5, nw, 1e-6, gh, gd, gv, gstate, ss, tseq, slots, 1, max_seq_len=T), flush),
+        _median_us(torch, lambda: ops.gla(proj, low, a2, a2b, 8.0, gd ** -0.5, nw, 1e-6, gh, gd, gv, gstate, ss, tseq, slots, 1, max_seq_len=T), flush),
         T * ((2 * HD + 2 * HV) * 2 + HD * 4 * 2 + HV * 4 * 2 + HV * 2), flops=T * HD * gv * 5.0, like="mamba2 (conv, scan, gated norm)")
     inner, ch = mh * mp, mh * mp + 2 * N
     mproj = torch.randn(T, inner + ch, device=dev).to(bf)
@@ -448,7 +448,7 @@ def lofirax_kernels(torch, size, hbm_gbs, tokens=PREFILL_TOKENS):
     proj1, low1 = torch.randn(B, 2 * HD + 2 * HV, device=dev).to(bf), f32(1, B, LOFIRAX_RANK)
     gstate64 = torch.zeros(B, HD * gv, device=dev)
     rec("gla, one token for each of 64 sequences",
-        _median_us(torch, lambda: ops.gla(proj1, low1, a2, a2b, 16.0, gd ** -0.5, nw, 1e-6, gh, gd, gv, gstate64, ss1, tseq1, tseq1, B), flush),
+        _median_us(torch, lambda: ops.gla(proj1, low1, a2, a2b, 8.0, gd ** -0.5, nw, 1e-6, gh, gd, gv, gstate64, ss1, tseq1, tseq1, B), flush),
         gstate64.numel() * 8, like="mamba2, one token for each of 64 sequences")
     mproj1, dtr1 = torch.randn(B, inner + ch, device=dev).to(bf), f32(B, mh)
     mstate64 = torch.zeros(B, ops.mamba2_state_size(mh, mp, N, 1, 4), device=dev)

@@ -104,7 +104,7 @@ def latent_attention(h, m: dict, t: Dict[str, torch.Tensor], p: str, eps: float,
     mx = torch.maximum(s.max(-1).values, sink[:, None].expand(H, T))
     e = torch.exp(s - mx[..., None])
     w = e / (e.sum(-1) + torch.exp(sink[:, None] - mx))[..., None]
-    o = rnd(torch.einsum("htn,nhv->thv", w, v).reshape(T, H * V))
+    o = rnd(torch.einsum("htn,nhv->thv", rnd(w), v).reshape(T, H * V))      # tensor-core kernels round the weights that meet v
     return o @ t[p + "o"].T, (c, k_rot)
 
 

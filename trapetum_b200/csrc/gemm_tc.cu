@@ -55,7 +55,8 @@ struct GemmParams {
     int act;                         // gated epilogue: 0 gelu_tanh, 1 silu, 2 clamped_swish (only with GATED kernels)
     float limit;                     // clamped_swish: both branches are bounded by it
     // Grouped products (token-major tiles only): tile tp of the tokens multiplies the weight rows of group
-    // tile_group[tp], which start at row tile_group[tp] * group_rows of the weight operand.  Null: one group.
+    // tile_group[tp], which start at row tile_group[tp] * group_rows of the weight operand; a negative entry: the tile
+    // is not in use and nobody touches it.  Null: one group.
     const int* tile_group;
     int group_rows;
 };
@@ -230,7 +231,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 if (!SWAP && p.tile_group != nullptr) {
                     // the table of groups is the preceding kernel's work: nothing is fetched before it is there
                     if (!waited) { pdl_wait(); waited = true; }
-                    w_row += p.tile_group[tp] * p.group_rows;
+                    const int g = p.tile_group[tp];
+                    if (g < 0) continue;               // a tile past the last one in use: all three roles leave it out
+                    w_row += g * p.group_rows;
                 }
                 int kb = kb0;
                 if (!waited) {
@@ -272,10 +275,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             constexpr uint32_t idesc = instr_desc(BN);
             uint32_t it = 0, tile_it = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, tile_it++) {
+            if (!SWAP && p.tile_group != nullptr) pdl_wait();      // the table of groups is the preceding kernel's work
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 int tp, tq, sp; decode(item, tp, tq, sp);
+                if (!SWAP && p.tile_group != nullptr && p.tile_group[tp] < 0) continue;
                 const int kb0 = sp * p.kb_per_split, kb1 = min(p.kblocks, kb0 + p.kb_per_split);
                 const int a = tile_it & 1; const uint32_t aph = (tile_it >> 1) & 1;
+                tile_it++;
                 if (*abort_flag || !mbar_wait(&acc_empty[a], aph ^ 1)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_addr = tmem_base + a * C::ACC_COLS;
@@ -303,9 +309,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         pdl_wait();                                    // the output may still be read by the kernel before
         uint32_t tile_it = 0;
         bool ok = true;
-        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, tile_it++) {
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             int tp, tq, sp; decode(item, tp, tq, sp);
+            if (!SWAP && p.tile_group != nullptr && p.tile_group[tp] < 0) continue;
             const int a = tile_it & 1; const uint32_t aph = (tile_it >> 1) & 1;
+            tile_it++;
             // the decision must be the same in every lane: tcgen05.ld is a warp-wide instruction
             const bool mine = !*abort_flag && mbar_wait(&acc_full[a], aph);
             if (!__all_sync(0xffffffffu, mine)) { ok = false; break; }
@@ -788,7 +796,7 @@ extern "C" int tb_gemm_tc_ex(const void* A, const void* W, void* C, int c_dtype,
 // W holds `groups` matrices of N rows each, one after the other ([groups * N, K]); rows of A are ordered so that every
 // tile of 128 belongs to one group.  gated_act >= 0: the gated epilogue on rows interleaved per group (N = 2 x the
 // output's width, bfloat16 out); else a plain product into C (bfloat16 or float32).  tile_group: device memory,
-// [ceil(M / 128)] group numbers in [0, groups).
+// [ceil(M / 128)] group numbers in [0, groups), or -1 for a tile that is not in use (its rows of C are not written).
 extern "C" int tb_gemm_tc_grouped(const void* A, const void* W, void* C, int c_dtype, int M, int N, int groups, int K,
                                   long long lda, long long ldw, long long ldc, const int* tile_group, int gated_act,
                                   cudaStream_t stream) {

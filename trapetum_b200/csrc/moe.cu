@@ -433,7 +433,7 @@ struct MoePadArgs {
     const int* idx;            // [P] expert of every pair
     int* pos;                  // [P] the pair's row in the padded order
     int* row_pair;             // [max_rows] the pair a row holds, -1 for padding
-    int* tile_group;           // [max_rows / 128] the tile's expert (0 for tiles past the last one)
+    int* tile_group;           // [max_rows / 128] the tile's expert (-1 for tiles past the last one: the product leaves them out)
     int P, E, max_rows;
 };
 
@@ -445,7 +445,7 @@ __global__ void __launch_bounds__(1024) moe_group_padded_kernel(MoePadArgs a) {
     __syncthreads();
     pdl_wait();
     for (int r = threadIdx.x; r < a.max_rows; r += blockDim.x) a.row_pair[r] = -1;
-    for (int t = threadIdx.x; t < a.max_rows / 128; t += blockDim.x) a.tile_group[t] = 0;
+    for (int t = threadIdx.x; t < a.max_rows / 128; t += blockDim.x) a.tile_group[t] = -1;     // not in use until an expert claims it
     for (int p = threadIdx.x; p < a.P; p += blockDim.x) atomicAdd(&cnt[a.idx[p]], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
