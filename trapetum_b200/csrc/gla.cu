@@ -236,11 +236,23 @@ __global__ void gla_fold_kernel(GlaArgs a) {
     const long long e = i % per;                      // (h, d, v)
     const long long hd = e / V;                       // h * D + d
     float S = a.state[(size_t)a.slot_ids[b] * a.state_stride + e];
-    for (int c = 0; c < a.n_chunks; c++) {
-        float* cs = a.chunk_state + ((size_t)b * a.n_chunks + c) * per + e;
-        const float E = *cs;
-        *cs = S;
-        S = fmaf(a.chunk_decay[((size_t)b * a.n_chunks + c) * a.heads * D + hd], S, E);
+    float* cs = a.chunk_state + (size_t)b * a.n_chunks * per + e;
+    const float* cd = a.chunk_decay + (size_t)b * a.n_chunks * a.heads * D + hd;
+    for (int c0 = 0; c0 < a.n_chunks; c0 += 8) {       // eight chunks' end states and decays on their way together
+        float E[8], P[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const bool in = c0 + u < a.n_chunks;
+            E[u] = in ? cs[(size_t)(c0 + u) * per] : 0.f;
+            P[u] = in ? cd[(size_t)(c0 + u) * a.heads * D] : 1.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            if (c0 + u < a.n_chunks) {
+                cs[(size_t)(c0 + u) * per] = S;
+                S = fmaf(P[u], S, E[u]);
+            }
+        }
     }
 }
 
